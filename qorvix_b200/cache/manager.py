@@ -53,6 +53,13 @@ class LayerCacheView:
     page_size: int = 0
 
 
+@dataclass
+class CompositeCacheView:
+    """What a mixer of several parts gets: one view per part, in the order of the tuple its cache_spec() returned."""
+    views: List[LayerCacheView]
+    kind: str = "composite"
+
+
 class _PoolView:
     """Read-only view of one paged group's pool in the native manager."""
 

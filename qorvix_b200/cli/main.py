@@ -88,7 +88,13 @@ def cmd_model_info(args) -> int:
         print("usage: qorvix model-info <model_dir>", file=sys.stderr)
         return 1
     cfg = load_config(args[1])
-    spec = lookup_architecture(cfg.architecture).build_spec(cfg)
+    from ..weights import Checkpoint
+    try:
+        ckpt = Checkpoint(args[1])
+        shapes = {n: tuple(ckpt.shape(n)) for n in ckpt.names()}
+    except ValueError:
+        shapes = None                              # a folder with a configuration only
+    spec = lookup_architecture(cfg.architecture).spec_for(cfg, shapes)
     n_params = 0
     for shape, _ in spec.tensor_table().values():
         k = 1

@@ -20,15 +20,23 @@ class ArchitectureEntry:
     config_from_dict: Callable[[dict], ModelConfig]
     build_spec: Callable[[ModelConfig], "object"]          # -> parts.spec.ModelSpec
     random_tensors: Callable[..., "object"] = None          # (config, seed, device) -> iterator of (name, tensor)
+    shapes_from_tensors: bool = False                       # build_spec(config, shapes): some sizes are given by stored tensors only
+
+    def spec_for(self, config, shapes=None):
+        """The ModelSpec of `config`; `shapes` (name -> shape of the stored tensors) goes to builders that read sizes from it."""
+        if self.shapes_from_tensors:
+            return self.build_spec(config, shapes)
+        return self.build_spec(config)
 
 
 _ARCHITECTURES: Dict[str, ArchitectureEntry] = {}
 
 
-def register_architecture(name: str, config_from_dict, build_spec, random_tensors=None, *, replace: bool = False) -> None:
+def register_architecture(name: str, config_from_dict, build_spec, random_tensors=None, *, replace: bool = False,
+                          shapes_from_tensors: bool = False) -> None:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture '{name}' is already registered")
-    _ARCHITECTURES[name] = ArchitectureEntry(name, config_from_dict, build_spec, random_tensors)
+    _ARCHITECTURES[name] = ArchitectureEntry(name, config_from_dict, build_spec, random_tensors, shapes_from_tensors)
 
 
 def unregister_architecture(name: str) -> None:

@@ -40,6 +40,8 @@ LIBRARIES = {
     "recurrent": "recurrent.cu",
     "moe": "moe.cu",
     "diff_attention": "diff_attention.cu",
+    "channel_scan": "channel_scan.cu",
+    "bias_attention": "bias_attention.cu",
     "host_runtime": "host_runtime.cpp",          # host-side cache bookkeeping: plain C++, no CUDA
     "ref": "ref/ref_model.cpp",                  # the kernels' plain C++ twins and a whole-model forward: host only
     "executor": "host/executor_api.cpp",         # the native step executor behind a C interface (host code, CUDA runtime calls)

@@ -542,6 +542,168 @@ extern "C" int qv_activation(void* out, const void* x, long long n, int kind, in
   return QV_ERR_UNSUPPORTED;
 }
 
+// ---------------------------------------------------------------- norm without statistics (Dynamic Tanh)
+// row r reads source row s = row_idx ? row_idx[r] : r.
+//   x = residual[s] + (delta ? delta[s] : 0)        (float32 sum; written back unless row_idx is given)
+//   out[r] = tanh(alpha * x) * w + b                (float32 arithmetic; no mean, no variance)
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256) add_tanhnorm_kernel(TO* __restrict__ out, float* __restrict__ residual, const TD* __restrict__ delta,
+                                                          const float* __restrict__ w, const float* __restrict__ b, float alpha,
+                                                          const int* __restrict__ row_idx, int d, int write_residual) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int s = row_idx ? row_idx[r] : r;
+  float* res = residual + (size_t)s * d;
+  const TD* dl = delta ? delta + (size_t)s * d : nullptr;
+  TO* o = out + (size_t)r * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = res[i];
+    if (dl) x += to_f(dl[i]);
+    if (write_residual && dl) res[i] = x;
+    o[i] = from_f<TO>(fmaf(tanhf(alpha * x), w[i], b ? b[i] : 0.f));
+  }
+}
+
+extern "C" int qv_add_tanhnorm(void* out, float* residual, const void* delta, const float* w, const float* b, float alpha,
+                               const int* row_idx, int rows, int d, int write_residual, int delta_dt, int out_dt, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH_TN(TD, TO)                                                                                                   \
+  return qv_launch(add_tanhnorm_kernel<TD, TO>, dim3(rows), dim3(256), 0, st, (TO*)out, residual, (const TD*)delta, w, b, alpha, \
+                   row_idx, d, write_residual)
+  if (delta_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_TN(float, float);
+  if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_TN(bf16, bf16);
+  if (delta_dt == QV_DT_F32 && out_dt == QV_DT_BF16) LAUNCH_TN(float, bf16);
+  if (delta_dt == QV_DT_BF16 && out_dt == QV_DT_F32) LAUNCH_TN(bf16, float);
+#undef LAUNCH_TN
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- token row + learned position row (+ tanh norm)
+// out[t] (float32) = table[ids[t]] + pos_scale * pos_table[tok_pos[t]], the sum in float32; with w also
+// out = tanh(alpha * out) * w + b.  Ids and positions outside their tables are clamped.
+template <typename TW>
+__global__ void __launch_bounds__(256) embed_pos_kernel(float* __restrict__ out, const TW* __restrict__ table, const TW* __restrict__ pos_table,
+                                                       const int* __restrict__ ids, const int* __restrict__ tok_pos, int d, int vocab,
+                                                       int positions, float pos_scale, const float* __restrict__ w,
+                                                       const float* __restrict__ b, float alpha) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  int id = ids[t], p = tok_pos[t];
+  id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+  p = p < 0 ? 0 : (p >= positions ? positions - 1 : p);
+  const TW* e = table + (size_t)id * d;
+  const TW* q = pos_table + (size_t)p * d;
+  float* o = out + (size_t)t * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float x = fmaf(pos_scale, to_f(q[i]), to_f(e[i]));
+    if (w) x = fmaf(tanhf(alpha * x), w[i], b ? b[i] : 0.f);
+    o[i] = x;
+  }
+}
+
+extern "C" int qv_embed_pos(float* out, const void* table, const void* pos_table, const int* ids, const int* tok_pos, int T, int d,
+                            int vocab, int positions, float pos_scale, const float* w, const float* b, float alpha, int table_dt,
+                            void* stream) {
+  if (T <= 0) return 0;
+  QV_DISPATCH_DT(table_dt, TW,
+                 return qv_launch(embed_pos_kernel<TW>, dim3(T), dim3(256), 0, (cudaStream_t)stream, out, (const TW*)table,
+                                  (const TW*)pos_table, ids, tok_pos, d, vocab, positions, pos_scale, w, b, alpha));
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- gated feed-forward activations
+// out[t, i] = act(gu[t, i]) * gu[t, f + i]; act 0: SiLU, 1: the tanh form of GELU.  Float32 arithmetic.
+template <typename T>
+__global__ void glu_act_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t n, int f, int act) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / f;
+    const int i = (int)(idx - t * f);
+    const float g = to_f(gu[t * 2 * f + i]);
+    const float u = to_f(gu[t * 2 * f + f + i]);
+    float a;
+    if (act == 1) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+    else a = g / (1.0f + expf(-g));
+    out[idx] = from_f<T>(a * u);
+  }
+}
+
+extern "C" int qv_glu_act(void* out, const void* gu, int T, int f, int act, int dt, void* stream) {
+  const size_t n = (size_t)T * f;
+  if (n == 0) return 0;
+  if (act != 0 && act != 1) return QV_ERR_UNSUPPORTED;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  QV_DISPATCH_DT(dt, TT, return qv_launch(glu_act_kernel<TT>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (TT*)out, (const TT*)gu, n, f, act));
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- gate of a sublayer's result
+// out[t, i] (float32) = y[t, i] * sigmoid(g[t, i] + bias[i]): y in float32 or the compute type (row stride ld_y), g
+// float32 pre-activations (row stride ld_g, so a column slice of a wider product serves).
+template <typename TY>
+__global__ void sigmoid_gate_kernel(float* __restrict__ out, const TY* __restrict__ y, int ld_y, const float* __restrict__ g, int ld_g,
+                                    const float* __restrict__ bias, size_t n, int d) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = idx / d;
+    const int i = (int)(idx - t * d);
+    const float z = g[t * ld_g + i] + (bias ? bias[i] : 0.f);
+    out[idx] = to_f(y[t * ld_y + i]) * (1.0f / (1.0f + expf(-z)));
+  }
+}
+
+extern "C" int qv_sigmoid_gate(float* out, const void* y, int ld_y, const float* g, int ld_g, const float* bias, int T, int d, int y_dt,
+                               void* stream) {
+  const size_t n = (size_t)T * d;
+  if (n == 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  QV_DISPATCH_DT(y_dt, TY, return qv_launch(sigmoid_gate_kernel<TY>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, out, (const TY*)y,
+                                            ld_y, g, ld_g, bias, n, d));
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- weighted sum over the streams kept so far
+// stack [slots][n] float32 keeps the embedding's output and every run's result.  The run's result, x + delta (delta may be null,
+// float32), goes into slot `count - 1`; x then becomes sum over j < count of w[j] * stack[j][.], added up in the order of j.
+__global__ void depth_mix_kernel(float* __restrict__ x, const float* __restrict__ delta, float* __restrict__ stack, size_t n,
+                                 const float* __restrict__ w, int count) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float cur = x[i];
+    if (delta) cur += delta[i];
+    stack[(size_t)(count - 1) * n + i] = cur;
+    float acc = 0.f;
+    for (int j = 0; j + 1 < count; ++j) acc = fmaf(w[j], stack[(size_t)j * n + i], acc);
+    x[i] = fmaf(w[count - 1], cur, acc);
+  }
+}
+
+extern "C" int qv_depth_mix(float* x, const float* delta, float* stack, long long n, const float* w, int count, void* stream) {
+  if (n <= 0) return 0;
+  if (count < 1) return QV_ERR_UNSUPPORTED;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  return qv_launch(depth_mix_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, delta, stack, (size_t)n, w, count);
+}
+
+// x *= s in place, float32 (a fixed factor on logits).
+__global__ void scale_kernel(float* __restrict__ x, size_t n, float s) {
+  pdl_wait();
+  pdl_launch_dependents();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) x[i] *= s;
+}
+
+extern "C" int qv_scale(float* x, long long n, float s, void* stream) {
+  if (n <= 0) return 0;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  return qv_launch(scale_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, (size_t)n, s);
+}
+
 extern "C" const char* qv_error_string(int code) {
   if (code == QV_ERR_UNSUPPORTED) return "size or dtype not supported by this kernel";
   if (code == QV_ERR_TOO_LARGE) return "size exceeds what this kernel can hold on chip";

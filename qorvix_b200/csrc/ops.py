@@ -82,11 +82,25 @@ _ARGTYPES = {
     "qv_diff_partial_floats": [_I],
     "qv_diff_attention_tc": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _V, _I, _V],
     "qv_diff_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _V],
+    "qv_add_tanhnorm": [_V, _V, _V, _V, _V, _F, _V, _I, _I, _I, _I, _I, _V],
+    "qv_embed_pos": [_V, _V, _V, _V, _V, _I, _I, _I, _I, _F, _V, _V, _F, _I, _V],
+    "qv_glu_act": [_V, _V, _I, _I, _I, _I, _V],
+    "qv_sigmoid_gate": [_V, _V, _I, _V, _I, _V, _I, _I, _I, _V],
+    "qv_depth_mix": [_V, _V, _V, _L, _V, _I, _V],
+    "qv_scale": [_V, _L, _F, _V],
+    "qv_channel_gates": [_V, _I, _V, _I, _V, _V, _I, _I, _I, _I, _I, _F, _V],
+    "qv_unit_keys": [_V, _V, _V, _I, _V, _I, _V, _I, _I, _I, _F, _V],
+    "qv_channel_scan_state_floats": [_I, _I, _I],
+    "qv_channel_scan": [_V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _F, _V, _L, _V, _V, _I, _I, _I, _I, _V],
+    "qv_head_norm_gate": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _F, _I, _V],
+    "qv_bias_attn_prepare": [_V, _I, _V, _I, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _V],
+    "qv_bias_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _V, _I, _V, _V, _I, _F, _I, _V],
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
 _RESTYPES = {"qv_error_string": ctypes.c_char_p, "qv_packed_weight_bytes": c_longlong, "qv_gemm_bf16_split_slot_bytes": c_longlong,
-             "qv_linear_scan_state_floats": c_longlong, "qv_latent_tc_workspace_bytes": c_longlong, "qv_diff_partial_floats": c_longlong}
+             "qv_linear_scan_state_floats": c_longlong, "qv_latent_tc_workspace_bytes": c_longlong, "qv_diff_partial_floats": c_longlong,
+             "qv_channel_scan_state_floats": c_longlong}
 _typed_libs = {}
 
 
@@ -326,6 +340,76 @@ def activation(out, x, kind: int = ACT_RELU2) -> None:
     _check(_lib("elementwise").qv_activation(_ptr(out), _ptr(x), x.numel(), kind, dt_code(x.dtype), _stream()), "activation")
 
 
+def add_tanhnorm(out, residual, delta, weight, bias, alpha: float, row_idx=None) -> None:
+    """residual (float32) += delta (None: nothing added); out = tanh(alpha * residual) * weight + bias.  With row_idx only
+    those rows of residual + delta are normed and the residual is left as it is."""
+    _need_cuda(out, residual, delta, weight, bias, row_idx)
+    d = residual.shape[1]
+    rows = residual.shape[0] if row_idx is None else row_idx.numel()
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (rows, d)
+    assert weight.dtype == torch.float32 and weight.numel() == d and (bias is None or (bias.dtype == torch.float32 and bias.numel() == d))
+    assert delta is None or (delta.is_contiguous() and delta.shape == residual.shape)
+    if row_idx is not None:
+        _i32(row_idx, "row_idx")
+    rc = _lib("elementwise").qv_add_tanhnorm(_ptr(out), _ptr(residual), _ptr(delta), _ptr(weight), _ptr(bias), float(alpha), _ptr(row_idx),
+                                             rows, d, 0 if row_idx is not None else 1, dt_code(delta.dtype) if delta is not None else F32,
+                                             dt_code(out.dtype), _stream())
+    _check(rc, "add_tanhnorm")
+
+
+def embed_pos(out, table, pos_table, ids, tok_pos, pos_scale: float = 1.0, weight=None, bias=None, alpha: float = 1.0) -> None:
+    """out[t] (float32) = table[ids[t]] + pos_scale * pos_table[tok_pos[t]]; with weight also tanh(alpha * out) * weight + bias."""
+    _need_cuda(out, table, pos_table, ids, tok_pos, weight, bias)
+    _i32(ids, "ids"); _i32(tok_pos, "tok_pos")
+    T, d = out.shape
+    assert out.dtype == torch.float32 and out.is_contiguous() and table.is_contiguous() and pos_table.is_contiguous()
+    assert table.dtype == pos_table.dtype and table.shape[1] == d == pos_table.shape[1]
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == d and (bias is None or bias.dtype == torch.float32))
+    rc = _lib("elementwise").qv_embed_pos(_ptr(out), _ptr(table), _ptr(pos_table), _ptr(ids), _ptr(tok_pos), T, d, table.shape[0],
+                                          pos_table.shape[0], float(pos_scale), _ptr(weight), _ptr(bias), float(alpha),
+                                          dt_code(table.dtype), _stream())
+    _check(rc, "embed_pos")
+
+
+GLU_SILU, GLU_GELU_TANH = 0, 1
+
+
+def glu_act(out, gu, act: int) -> None:
+    """out[t, i] = act(gu[t, i]) * gu[t, f + i]; act GLU_SILU or GLU_GELU_TANH."""
+    _need_cuda(out, gu)
+    T, f = out.shape
+    assert out.dtype == gu.dtype and out.is_contiguous() and gu.is_contiguous() and tuple(gu.shape) == (T, 2 * f)
+    _check(_lib("elementwise").qv_glu_act(_ptr(out), _ptr(gu), T, f, act, dt_code(out.dtype), _stream()), "glu_act")
+
+
+def sigmoid_gate(out, y, g, bias) -> None:
+    """out (float32 [T, d]) = y * sigmoid(g + bias): y float32 or the compute type, g float32 (column slices are fine)."""
+    _need_cuda(out, y, g, bias)
+    T, d = out.shape
+    assert out.dtype == g.dtype == torch.float32 and out.is_contiguous() and y.stride(1) == 1 and g.stride(1) == 1
+    assert tuple(y.shape) == tuple(g.shape) == (T, d) and (bias is None or (bias.dtype == torch.float32 and bias.numel() == d))
+    rc = _lib("elementwise").qv_sigmoid_gate(_ptr(out), _ptr(y), y.stride(0), _ptr(g), g.stride(0), _ptr(bias), T, d, dt_code(y.dtype),
+                                             _stream())
+    _check(rc, "sigmoid_gate")
+
+
+def depth_mix(x, delta, stack, weights, count: int) -> None:
+    """stack[count - 1] = x + delta (float32; delta may be None); x = sum over j < count of weights[j] * stack[j]."""
+    _need_cuda(x, delta, stack, weights)
+    n = x.numel()
+    assert x.dtype == stack.dtype == weights.dtype == torch.float32 and x.is_contiguous() and stack.is_contiguous()
+    assert stack.shape[0] >= count and stack[0].numel() == n and weights.numel() >= count
+    assert delta is None or (delta.dtype == torch.float32 and delta.is_contiguous() and delta.numel() == n)
+    _check(_lib("elementwise").qv_depth_mix(_ptr(x), _ptr(delta), _ptr(stack), n, _ptr(weights), count, _stream()), "depth_mix")
+
+
+def scale(x, s: float) -> None:
+    """x *= s in place (float32)."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    _check(_lib("elementwise").qv_scale(_ptr(x), x.numel(), float(s), _stream()), "scale")
+
+
 # ------------------------------------------------------------------ differential attention
 
 def diff_prepare(q_out, proj, bias, q_weight, k_weight, eps, cos_sin, ctx, block_table, cache_layer, H, G, n, dv, rot, page) -> None:
@@ -559,6 +643,112 @@ def gated_group_norm(out, y, gate, w, groups: int, eps: float, gate_first: bool)
     rc = _lib("recurrent").qv_gated_group_norm(_ptr(out), out.stride(0), _ptr(y), y.stride(0), _ptr(gate), gate.stride(0), _ptr(w),
                                                T, W, groups, eps, 1 if gate_first else 0, dt_code(out.dtype), _stream())
     _check(rc, "gated_group_norm")
+
+
+# ------------------------------------------------------------------ recurrences with a decay per key channel
+
+GATE_POW_SIGMOID, GATE_EXP_NEG_SIGMOID = 0, 1
+HEAD_GATE_SIGMOID, HEAD_GATE_SILU = 0, 1
+
+
+def channel_gates(out, x1, w2, bias, pre_tanh: bool, kind: int, p: float) -> None:
+    """out[t, c] (float32) = g(sum_r f(x1[t, r]) w2[c, r] + bias[c]): f the identity or tanh; g(z) = sigmoid(z)^p
+    (GATE_POW_SIGMOID) or exp(-p sigmoid(z)) (GATE_EXP_NEG_SIGMOID).  x1 float32 [T, R] (a column slice is fine),
+    w2 float32 [N, R]."""
+    _need_cuda(out, x1, w2, bias)
+    T, R = x1.shape
+    N = w2.shape[0]
+    assert out.dtype == x1.dtype == w2.dtype == torch.float32 and out.stride(1) == 1 and x1.stride(1) == 1 and w2.is_contiguous()
+    assert tuple(out.shape) == (T, N) and w2.shape[1] == R and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))
+    rc = _lib("channel_scan").qv_channel_gates(_ptr(out), out.stride(0), _ptr(x1), x1.stride(0), _ptr(w2), _ptr(bias), T, N, R,
+                                               1 if pre_tanh else 0, kind, float(p), _stream())
+    _check(rc, "channel_gates")
+
+
+def unit_keys(u, au, k, a, a_bias, H: int, n: int, eps: float) -> None:
+    """Per token and head: u = k / sqrt(sum(k^2) + eps), au = sigmoid(a + a_bias) * u; k, a float32 [T, H*n] (column
+    slices are fine), u, au dense float32 [T, H*n]."""
+    _need_cuda(u, au, k, a, a_bias)
+    T = k.shape[0]
+    assert k.dtype == a.dtype == u.dtype == au.dtype == torch.float32 and k.stride(1) == 1 and a.stride(1) == 1
+    assert u.is_contiguous() and au.is_contiguous() and tuple(u.shape) == tuple(au.shape) == (T, H * n)
+    assert a_bias is None or (a_bias.dtype == torch.float32 and a_bias.numel() == H * n)
+    rc = _lib("channel_scan").qv_unit_keys(_ptr(u), _ptr(au), _ptr(k), k.stride(0), _ptr(a), a.stride(0), _ptr(a_bias), T, H, n,
+                                           float(eps), _stream())
+    _check(rc, "unit_keys")
+
+
+def channel_scan_state_floats(H: int, dk: int, dv: int) -> int:
+    """How many float32 values channel_scan keeps per request for H heads of dk x dv."""
+    return int(_lib("channel_scan").qv_channel_scan_state_floats(H, dk, dv))
+
+
+def channel_scan(out, q, k, v, w, au, u, q_scale: float, state, ctx, H: int, dk: int, dv: int) -> None:
+    """Per request and head: S = diag(w) S - au (u^T S) + k v^T (au, u None: no removal), out = S^T q * q_scale; all
+    operands float32, q, k, w, au, u [T, H*dk] and v [T, H*dv] (column slices are fine); state [slots, n] float32 is
+    read and left up to date."""
+    _need_cuda(out, q, k, v, w, au, u, state)
+    for x in (out, q, k, v, w, au, u):
+        assert x is None or (x.dtype == torch.float32 and x.stride(1) == 1)
+    assert state.dtype == torch.float32 and state.stride(-1) == 1 and state.shape[-1] >= H * dk * dv
+    rc = _lib("channel_scan").qv_channel_scan(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(w), w.stride(0), _ptr(au),
+        au.stride(0) if au is not None else 0, _ptr(u), u.stride(0) if u is not None else 0, float(q_scale), _ptr(state),
+        state.stride(0), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), ctx.num_segments, H, dk, dv, _stream())
+    _check(rc, "channel_scan")
+
+
+def head_norm_gate(out, y, gate, w, H: int, eps: float, gate_kind: int, factor: float = 1.0) -> None:
+    """out = y over its root mean square per head, times w (float32 [H*dv]), times sigmoid or SiLU of gate (float32),
+    times factor; y float32 [T, H*dv]; out (compute type) and gate may be column slices."""
+    _need_cuda(out, y, gate, w)
+    T, W = y.shape
+    assert W % H == 0 and y.dtype == gate.dtype == w.dtype == torch.float32 and w.numel() == W
+    assert y.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == T and out.shape[1] == W
+    rc = _lib("channel_scan").qv_head_norm_gate(_ptr(out), out.stride(0), _ptr(y), y.stride(0), _ptr(gate), gate.stride(0), _ptr(w), T, H,
+                                                W // H, float(eps), gate_kind, float(factor), dt_code(out.dtype), _stream())
+    _check(rc, "head_norm_gate")
+
+
+# ------------------------------------------------------------------ attention with a learned distance bias
+
+def bias_attn_prepare(q_out, proj, q_off, k_off, v_off, bq, bk, bv, cache_layer, ctx, block_table, H, G, n, dv, page, coef, every) -> None:
+    """From a float32 product's row [.. q .. k .. v ..]: q_out = (q + bq) * (1 + coef ln(floor((pos + 1) / every) + 1)) in the
+    compute type; k + bk and v + bv go into the token's cache row [G*n | G*dv]."""
+    _need_cuda(q_out, proj, bq, bk, bv, cache_layer, block_table)
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.dtype == cache_layer.dtype
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (n + dv))
+    for b, size in ((bq, H * n), (bk, G * n), (bv, G * dv)):
+        assert b is None or (b.dtype == torch.float32 and b.numel() == size)
+    _i32(block_table, "block_table")
+    rc = _lib("bias_attention").qv_bias_attn_prepare(
+        _ptr(q_out), q_out.stride(0), _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(bq), _ptr(bk), _ptr(bv), _ptr(cache_layer),
+        _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table), block_table.shape[-1], T, H, G, n, dv, page, float(coef), int(every),
+        dt_code(q_out.dtype), _stream())
+    _check(rc, "bias_attn_prepare")
+
+
+def bias_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor) -> None:
+    """out[t, h] = softmax_j((q_t,h . k_j) * scale + bias[bucket[min(i - j, len(bucket) - 1)], h]) v_j over the request's pages,
+    times sigmoid(gate[t, h]) (float32, or None) and factor."""
+    _need_cuda(out, q, cache_layer, block_table, bucket, bias, gate)
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == cache_layer.dtype
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (n + dv))
+    assert bucket.dtype == torch.int32 and bucket.is_contiguous() and bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[1] == H
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    _i32(block_table, "block_table")
+    rc = _lib("bias_attention").qv_bias_attention_generic(
+        _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table),
+        block_table.shape[-1], T, H, G, n, dv, page, float(scale), _ptr(bucket), bucket.numel() - 1, _ptr(bias), _ptr(gate),
+        gate.stride(0) if gate is not None else 0, float(factor), dt_code(q.dtype), _stream())
+    _check(rc, "bias_attention_generic")
+
+
+def bias_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor) -> None:
+    """Attention with a distance bias for every token of the step (see bias_attention_generic)."""
+    bias_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor)
 
 
 # ------------------------------------------------------------------ routed feed-forward

@@ -97,12 +97,14 @@ class NativeExecutor:
         from ..parts.rotary import RotaryEmbedding
         if not enabled() or model.order != list(range(len(model.blocks))) or type(model.final_norm) is not RMSNorm:
             return None
-        if getattr(model, "embedder", None) is not None or getattr(model.spec, "logit_softcap", 0.0):
+        if (getattr(model, "embedder", None) is not None or getattr(model.spec, "logit_softcap", 0.0)
+                or getattr(model.spec, "logit_scale", 1.0) != 1.0 or getattr(model.spec, "depth_average", None) is not None):
             return None
         rt = model.rt
         layers, keep, group, table = [], [], None, None
         for run, b in enumerate(model.blocks):
-            if type(b) is not PreNormBlock or type(b.mixer) is not Attention or type(b.feed_forward) is not SwiGLU:
+            if (type(b) is not PreNormBlock or type(b.mixer) is not Attention or type(b.feed_forward) is not SwiGLU
+                    or b.feed_forward.act != ops.GLU_SILU):
                 return None
             if type(b.mixer_norm) is not RMSNorm or type(b.ffn_norm) is not RMSNorm or type(b.mixer.position) is not RotaryEmbedding:
                 return None

@@ -55,7 +55,7 @@ class ModelRunner:
             self.config = config
             source = TensorSource(tensors=tensors, device=self.device, compute_dtype=self.dtype, where="tensors in memory")
         entry = lookup_architecture(self.config.architecture)
-        self.spec = entry.build_spec(self.config)
+        self.spec = entry.spec_for(self.config, {n: tuple(source.shape(n)) for n in source.names()})
         self.page_size = int(page_size)
         pool_tokens = -(-int(max_tokens) // self.page_size) * self.page_size
         limit = self.spec.max_position if self.spec.max_position else pool_tokens

@@ -32,6 +32,9 @@ class TextModel:
         self.order: List[int] = list(spec.order)
         # a stretch of layers that runs again: where the stream re-enters it (None: no such stretch)
         self.loop = build_part("stream", getattr(spec, "loop", None), source, rt)
+        # the stream after each run as a weighted sum of all runs' results (None: the run's result as it is)
+        self.depth = build_part("stream", getattr(spec, "depth_average", None), source, rt)
+        self._more_views = {}          # run -> the indices of the further caches of a mixer that keeps several
         self.stream_tap = None         # callable(run, residual, pending) after every run: for tests and debugging
         self._native = None            # the native executor of this model over a cache, made on first use (False: not applicable)
 
@@ -41,10 +44,14 @@ class TextModel:
         run: in a later step its first run must find the keys its first run wrote, not its second's.
         A mixer that reads another layer's cache reads that layer's latest run before its own."""
         needs = []
+        more = []                                  # (run, further specs) of mixers that keep several caches
         last_run_of = {}
         for run, li in enumerate(self.order):
             m = getattr(self.blocks[li], "mixer", None)
             spec = m.cache_spec() if m is not None else None
+            if isinstance(spec, (tuple, list)):    # a mixer of several parts: the first is the run's own entry
+                more.append((run, list(spec[1:])))
+                spec = spec[0]
             src = m.reads_cache_of() if m is not None else None
             src_run = None
             if src is not None:
@@ -53,9 +60,22 @@ class TextModel:
                 src_run = last_run_of[src]
             needs.append((spec, src_run))
             last_run_of[li] = run
-        if self.embedder is not None:              # the embedding's own state comes after the runs
-            needs.append((self.embedder.cache_spec(), None))
+        if self.embedder is not None or more:      # the embedding's own state comes after the runs
+            needs.append((self.embedder.cache_spec() if self.embedder is not None else None, None))
+        self._more_views = {}
+        for run, specs in more:                    # then the further caches, which the run's view lists
+            self._more_views[run] = list(range(len(needs), len(needs) + len(specs)))
+            needs.extend((sp, None) for sp in specs)
         return needs
+
+    def _view(self, cache, run: int):
+        """What run `run` sees of the cache: its layer's view, or one view per part of a mixer that keeps several."""
+        view = cache.layer_view(run)
+        extra = self._more_views.get(run)
+        if not extra:
+            return view
+        from ..cache.manager import CompositeCacheView
+        return CompositeCacheView(views=[view] + [cache.layer_view(i) for i in extra])
 
     def forward(self, ctx, cache) -> Optional[torch.Tensor]:
         """Runs the tokens of `ctx`; returns float32 logits [wanted rows, vocab] (None if none wanted)."""
@@ -76,6 +96,7 @@ class TextModel:
         if self.loop is not None:                  # the embedding's output, kept for the passes' re-entries
             x0 = torch.empty_like(residual)
             ops.cast_rows(x0, residual)
+        stack = self.depth.begin(residual) if self.depth is not None else None
         for run, li in enumerate(self.order):
             if self.loop is not None and run in self.loop.pass_of:
                 residual, pending = self.loop.forward(run, residual, pending, x0), None
@@ -83,7 +104,9 @@ class TextModel:
             # none after the last block: the final norm gathers the wanted rows
             nxt = self.blocks[self.order[run + 1]] if run + 1 < len(self.order) else None
             ctx.next_norm = nxt.first_norm() if hasattr(nxt, "first_norm") else None
-            residual, pending = self.blocks[li].forward(residual, pending, ctx, cache.layer_view(run))
+            residual, pending = self.blocks[li].forward(residual, pending, ctx, self._view(cache, run))
+            if self.depth is not None:
+                residual, pending = self.depth.after(run, residual, pending, stack), None
             if self.stream_tap is not None:
                 self.stream_tap(run, residual, pending)
         if ctx.num_wanted == 0:
@@ -92,6 +115,8 @@ class TextModel:
         logits = self.lm_head(h, out_dtype=torch.float32)
         if self.spec.logit_softcap:
             ops.softcap(logits, self.spec.logit_softcap)
+        if getattr(self.spec, "logit_scale", 1.0) != 1.0:
+            ops.scale(logits, self.spec.logit_scale)
         return logits
 
 
@@ -104,3 +129,4 @@ class _BlockView:
         self.mixer_norm, self.ffn_norm = layer.mixer_norm, layer.ffn_norm
         self.mixer_scale, self.ffn_scale = getattr(layer, "mixer_scale", None), getattr(layer, "ffn_scale", None)
         self.residual_mult = getattr(layer, "residual_mult", 1.0)
+        self.mixer_gate, self.ffn_gate = getattr(layer, "mixer_gate", None), getattr(layer, "ffn_gate", None)

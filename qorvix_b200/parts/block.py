@@ -8,6 +8,7 @@ import torch
 
 from ..csrc import ops
 from .base import Block, PreNormed
+from .linear import Linear
 from .registry import build_part, register_part
 
 
@@ -120,5 +121,62 @@ class ParallelBlock(Block):
         return None                              # two norms read the stream: nothing for the block ahead to prepare
 
 
+class GatedPreNormBlock(Block):
+    """x += mixer(h) * sigmoid(W1 h + b1), h = norm_a(x);  x += feed_forward(h) * sigmoid(W2 h + b2), h = norm_b(x): the
+    pre-norm block with a gate on each part's result, computed from the part's own input.  The gates' pre-activations leave
+    their products in float32; sigmoid, the multiplication and the residual sum are float32.  A mixer that shares its input
+    product (parts/shared_io.py) takes the gate's rows into it."""
+
+    def __init__(self, spec, source, rt):
+        self.rt = rt
+        self.mixer_norm = build_part("norm", spec.mixer_norm, source, rt)
+        self.mixer = build_part("mixer", spec.mixer, source, rt)
+        self.feed_forward = build_part("feed_forward", spec.feed_forward, source, rt)
+        self.ffn_norm = build_part("norm", spec.ffn_norm, source, rt) if self.feed_forward is not None else None
+        self.mixer_gate = self.ffn_gate = None
+        self.mixer_gate_bias = self.ffn_gate_bias = None
+        self.gate_in_mixer = False
+        name = getattr(spec, "mixer_gate", None)
+        if self.mixer is not None and name is not None:
+            self.mixer_gate_bias = source.get(name + ".b", dtype=torch.float32)
+            if hasattr(self.mixer, "take_extra_rows") and getattr(self.mixer, "shared", True):
+                self.mixer.take_extra_rows(source.get(name))
+                self.gate_in_mixer = True
+            else:
+                self.mixer_gate = Linear(source.get(name))
+        name = getattr(spec, "ffn_gate", None)
+        if self.feed_forward is not None and name is not None:
+            self.ffn_gate = Linear(source.get(name))
+            self.ffn_gate_bias = source.get(name + ".b", dtype=torch.float32)
+
+    def forward(self, residual, pending, ctx, cache):
+        if isinstance(pending, PreNormed):
+            pending = None                       # the product is in the stream already
+        if self.mixer is not None:
+            h = self.mixer_norm.add_norm(residual, pending)
+            y = self.mixer.forward(h, ctx, cache)
+            if self.gate_in_mixer:
+                pending = self._gated(y, self.mixer.extra_out, self.mixer_gate_bias)
+            elif self.mixer_gate is not None:
+                pending = self._gated(y, self.mixer_gate(h, out_dtype=torch.float32), self.mixer_gate_bias)
+            else:
+                pending = y
+        if self.feed_forward is not None:
+            h = self.ffn_norm.add_norm(residual, pending)
+            y = self.feed_forward.forward(h, ctx)
+            pending = self._gated(y, self.ffn_gate(h, out_dtype=torch.float32), self.ffn_gate_bias) if self.ffn_gate is not None else y
+        return residual, pending
+
+    @staticmethod
+    def _gated(y, pre, bias):
+        out = torch.empty(y.shape, device=y.device, dtype=torch.float32)
+        ops.sigmoid_gate(out, y, pre, bias)
+        return out
+
+    def first_norm(self):
+        return None                              # its norms do not fold into products
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "gated_pre_norm", GatedPreNormBlock)
 register_part("block", "parallel", ParallelBlock)

@@ -33,4 +33,33 @@ class BigramEmbedding:
         ops.embed_pair(out, self.table, self.pair, ctx.token_ids, ctx, cache.tensor.reshape(-1), s.buckets, s.mul_prev, s.mul_cur)
 
 
+class PositionedEmbedding:
+    """Token row plus the row of a learned position table, the sum (float32) optionally through a tanh norm; one kernel.
+    It keeps no state: the position of a token is the step's."""
+
+    def __init__(self, spec, source, rt):
+        self.spec = spec
+        self.table = source.get(spec.table)
+        self.pos = source.get(spec.pos_table)
+        if self.pos.dtype != self.table.dtype:
+            self.pos = self.pos.to(self.table.dtype)
+        self.norm_w = self.norm_b = None
+        self.alpha = 1.0
+        if spec.norm is not None:
+            self.norm_w = source.get(spec.norm.weight, dtype=torch.float32)
+            self.norm_b = source.get(spec.norm.bias, dtype=torch.float32)
+            self.alpha = float(source.get(spec.norm.alpha, dtype=torch.float32).reshape(-1)[0].item())
+
+    @property
+    def weight(self) -> torch.Tensor:
+        return self.table
+
+    def cache_spec(self):
+        return None
+
+    def forward(self, out, ctx, cache) -> None:
+        ops.embed_pos(out, self.table, self.pos, ctx.token_ids, ctx.tok_pos, self.spec.pos_scale, self.norm_w, self.norm_b, self.alpha)
+
+
 register_part("embedding", "bigram_embedding", BigramEmbedding)
+register_part("embedding", "positioned_embedding", PositionedEmbedding)

@@ -1,5 +1,5 @@
-"""SwiGLU feed-forward: down(silu(gate x) * up x), dense, no bias
-(reference: runtime/src/text_model.cpp:162-168, runtime/src/ops.cpp:96-100).  gate and up
+"""Gated feed-forward: down(act(gate x) * up x), dense, no bias; act is SiLU
+(reference: runtime/src/text_model.cpp:162-168, runtime/src/ops.cpp:96-100) or the tanh form of GELU.  gate and up
 are one fused projection."""
 from __future__ import annotations
 
@@ -20,7 +20,12 @@ class SwiGLU(FeedForward):
         # When the width allows, gate and up rows are interleaved in groups of 16 (16 gate rows, the 16
         # up rows of the same features, ...), so that one tile of the product holds both halves of a
         # feature and the activation is applied in the product's epilogue.
-        self.interleaved = self.f % 16 == 0
+        acts = {"silu": ops.GLU_SILU, "gelu_tanh": ops.GLU_GELU_TANH}
+        name = getattr(spec, "activation", "silu")
+        if name not in acts:
+            raise ValueError(f"unknown activation '{name}' (known: {', '.join(acts)})")
+        self.act = acts[name]
+        self.interleaved = self.f % 16 == 0 and self.act == ops.GLU_SILU      # the products' epilogue applies SiLU only
         if self.interleaved:
             k = g.shape[1]
             fused = torch.stack([g.to(dt).view(self.f // 16, 16, k), u.to(dt).view(self.f // 16, 16, k)], dim=1)
@@ -48,7 +53,7 @@ class SwiGLU(FeedForward):
                 ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed, self.gate_up.out_features)
             else:
                 gu = self.gate_up(x, out_dtype=self.rt.dtype)
-                ops.swiglu(act, gu)
+                ops.glu_act(act, gu, self.act)
         if residual is not None and next_norm is not None:
             pre = self.down.forward_to_stream(act, residual, next_norm)
             if pre is not None:

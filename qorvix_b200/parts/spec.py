@@ -82,13 +82,14 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """Dense gated feed-forward: down(silu(gate x) * up x)."""
+    """Dense gated feed-forward: down(act(gate x) * up x); act 'silu' or 'gelu_tanh' (the tanh form of GELU)."""
     hidden_size: int
     intermediate_size: int
     gate_proj: str
     up_proj: str
     down_proj: str
     kind: str = "swiglu"
+    activation: str = "silu"
 
     def tensors(self) -> TensorTable:
         return {self.gate_proj: ((self.intermediate_size, self.hidden_size), "matrix"),
@@ -359,13 +360,183 @@ class LoopSpec:
 
 
 @dataclass(frozen=True)
+class TanhNormSpec:
+    """Norm without statistics: tanh(alpha x) w + b with a scalar alpha, stored beside the weight as <weight>.alpha and <weight>.b."""
+    size: int
+    weight: str
+    kind: str = "tanh_norm"
+
+    @property
+    def bias(self) -> str:
+        return self.weight + ".b"
+
+    @property
+    def alpha(self) -> str:
+        return self.weight + ".alpha"
+
+    def tensors(self) -> TensorTable:
+        return {self.weight: ((self.size,), "norm"), self.bias: ((self.size,), "normal:0:0.1"), self.alpha: ((), "normal:0.7:0.1")}
+
+
+@dataclass(frozen=True)
+class PositionedEmbeddingSpec:
+    """Token row plus the row of a learned position table (times pos_scale), then an optional norm of the sum."""
+    vocab_size: int
+    hidden_size: int
+    positions: int
+    table: str
+    pos_table: str
+    norm: Optional[object] = None             # a TanhNormSpec, or None
+    pos_scale: float = 1.0
+    kind: str = "positioned_embedding"
+
+    def tensors(self) -> TensorTable:
+        t: TensorTable = {self.table: ((self.vocab_size, self.hidden_size), "matrix"),
+                          self.pos_table: ((self.positions, self.hidden_size), "matrix")}
+        if self.norm is not None:
+            t.update(self.norm.tensors())
+        return t
+
+
+@dataclass(frozen=True)
+class ChannelDecaySpec:
+    """A decay per head and key channel from a low-rank product: z = W2 f(W1 h) + bias, f the identity or tanh, then
+    'pow_sigmoid': sigmoid(z)^(1/tau), or 'exp_neg_sigmoid': exp(-rate * sigmoid(z))."""
+    rank: int
+    down: str                     # W1 [rank, hidden]
+    up: str                       # W2 [heads * key_dim, rank]
+    bias: str                     # [heads * key_dim]
+    form: str                     # "pow_sigmoid" | "exp_neg_sigmoid"
+    param: float                  # tau | rate
+    inner_tanh: bool = False
+
+
+@dataclass(frozen=True)
+class GLASpec:
+    """Gated linear attention: per head a key_dim x value_dim state, S = diag(decay) S + k v^T, o = S^T q with q scaled by
+    key_dim^(-1/2); each head's o is RMS-normed over value_dim with a weight shared by the heads, gated by SiLU of a
+    projection and projected."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    decay: ChannelDecaySpec
+    norm: str                     # [value_dim]
+    o_proj: str
+    kind: str = "gla"
+
+    def tensors(self) -> TensorTable:
+        H, d, dk, dv, dc = self.num_heads, self.hidden_size, self.key_dim, self.value_dim, self.decay
+        return {self.q_proj: ((H * dk, d), "matrix"), self.k_proj: ((H * dk, d), "matrix"), self.v_proj: ((H * dv, d), "matrix"),
+                self.gate_proj: ((H * dv, d), "matrix"), self.o_proj: ((d, H * dv), "matrix"), self.norm: ((dv,), "norm"),
+                dc.down: ((dc.rank, d), "matrix"), dc.up: ((H * dk, dc.rank), "normal:0:0.3"), dc.bias: ((H * dk,), "normal:2:1")}
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """Generalized delta rule: per head a dim x dim state, S = diag(w) S - (a u)(u^T S) + k v^T with u the key over its
+    length (key_eps under the root) and a = sigmoid(W_a h + b) the removal rate per key channel, both first terms reading
+    the old state; o = S^T r is divided by its root mean square per head, weighted over all heads' entries, gated by
+    the sigmoid of a projection and projected."""
+    hidden_size: int
+    num_heads: int
+    head_dim: int
+    eps: float
+    r_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    a_proj: str                   # bias: name + ".b"
+    decay: ChannelDecaySpec
+    norm: str                     # [heads * head_dim]
+    o_proj: str
+    key_eps: float = 1e-6
+    kind: str = "delta_rule"
+
+    def tensors(self) -> TensorTable:
+        H, d, n, dc = self.num_heads, self.hidden_size, self.head_dim, self.decay
+        t: TensorTable = {name: ((H * n, d), "matrix") for name in (self.r_proj, self.k_proj, self.v_proj, self.gate_proj, self.a_proj)}
+        t.update({self.a_proj + ".b": ((H * n,), "normal:0:0.5"), self.norm: ((H * n,), "norm"), self.o_proj: ((d, H * n), "matrix"),
+                  dc.down: ((dc.rank, d), "matrix"), dc.up: ((H * n, dc.rank), "normal:0:0.3"), dc.bias: ((H * n,), "normal:0:1")})
+        return t
+
+
+@dataclass(frozen=True)
+class BiasedAttentionSpec:
+    """Causal grouped-query softmax attention without rotation.  Positions enter through a learned bias on the scores,
+    bias[bucket(i - j), head] with `bias_rows` rows (one per distance below half the rows, the rest spaced evenly in the
+    logarithm of the distance up to bias_max), and through a temperature on the query, 1 + temp_coef ln(floor((p + 1) /
+    temp_every) + 1).  q, k, v and the output projection have biases (name + ".b"); the heads' outputs are multiplied by
+    the sigmoid of a projection of the mixer's input."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    bias_rows: int
+    bias_max: float
+    temp_coef: float
+    temp_every: int
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    gate_proj: str
+    rel_bias: str
+    o_proj: str
+    kind: str = "biased_attention"
+
+    def tensors(self) -> TensorTable:
+        H, G, n, dv, d = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size
+        return {self.q_proj: ((H * n, d), "matrix"), self.q_proj + ".b": ((H * n,), "normal:0:0.02"),
+                self.k_proj: ((G * n, d), "matrix"), self.k_proj + ".b": ((G * n,), "normal:0:0.02"),
+                self.v_proj: ((G * dv, d), "matrix"), self.v_proj + ".b": ((G * dv,), "normal:0:0.02"),
+                self.gate_proj: ((H * dv, d), "matrix"), self.rel_bias: ((self.bias_rows, H), "normal:0:0.5"),
+                self.o_proj: ((d, H * dv), "matrix"), self.o_proj + ".b": ((d,), "normal:0:0.02")}
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; the result is left_scale * left + right_scale * right."""
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    kind: str = "side_by_side"
+
+    def tensors(self) -> TensorTable:
+        t = dict(self.left.tensors())
+        t.update(self.right.tensors())
+        return t
+
+
+@dataclass(frozen=True)
+class DepthAverageSpec:
+    """After run i of the execution order the stream becomes a weighted sum of the embedding's output and the results of
+    runs 0..i (each taken before this averaging): weights[i] names a vector of i + 2 factors."""
+    weights: Tuple[str, ...]
+    hidden_size: int
+    kind: str = "depth_average"
+
+    def tensors(self) -> TensorTable:
+        return {name: ((i + 2,), "normal:0.3:0.2") for i, name in enumerate(self.weights)}
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One block: which parts and how they are arranged ('pre_norm': x += mixer(norm(x));
     x += ffn(norm(x)), the reference's order, runtime/src/text_model.cpp:146-168; 'parallel':
     x += mixer(norm_a(x)) + ffn(norm_b(x)), both reading the stream as it enters; a parallel block whose
     ffn_norm is None while it has a feed-forward gives both parts the one normed input).
     mixer_scale / ffn_scale name per-feature factors of the two parts' outputs ("layer scale") and
-    residual_mult multiplies what the block adds to the stream; the parallel block applies them."""
+    residual_mult multiplies what the block adds to the stream; the parallel block applies them.
+    'gated_pre_norm' is 'pre_norm' with each part's output multiplied by sigmoid(W h + b), h being the part's input:
+    mixer_gate / ffn_gate name W [width, width], the bias is name + ".b"."""
     mixer: object
     feed_forward: object
     mixer_norm: object
@@ -374,6 +545,8 @@ class LayerSpec:
     mixer_scale: Optional[str] = None
     ffn_scale: Optional[str] = None
     residual_mult: float = 1.0
+    mixer_gate: Optional[str] = None
+    ffn_gate: Optional[str] = None
 
     def tensors(self) -> TensorTable:
         t: TensorTable = {}
@@ -381,6 +554,10 @@ class LayerSpec:
             if part is not None:
                 t.update(part.tensors())
         width = getattr(self.mixer_norm, "size", None)
+        for name in (self.mixer_gate, self.ffn_gate):
+            if name is not None:
+                t[name] = ((width, width), "matrix")
+                t[name + ".b"] = ((width,), "normal:0:0.5")
         for name in (self.mixer_scale, self.ffn_scale):
             if name is not None:
                 t[name] = ((width,), "norm")
@@ -403,6 +580,8 @@ class ModelSpec:
     max_position: int = 0
     logit_softcap: float = 0.0                # > 0: logits = cap * tanh(logits / cap)
     loop: Optional[LoopSpec] = None           # where and how the stream re-enters a stretch of layers that runs again
+    logit_scale: float = 1.0                  # a fixed factor on the logits
+    depth_average: Optional[DepthAverageSpec] = None    # the stream after each run as a weighted sum of the runs' results
 
     def __post_init__(self):
         if self.order is None:
@@ -421,6 +600,8 @@ class ModelSpec:
         t.update(self.final_norm.tensors())
         if self.loop is not None:
             t.update(self.loop.tensors())
+        if self.depth_average is not None:
+            t.update(self.depth_average.tensors())
         if self.lm_head is not None:
             t[self.lm_head] = ((self.vocab_size, self.hidden_size), "matrix")
         return t

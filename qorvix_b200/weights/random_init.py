@@ -52,7 +52,7 @@ def draw_tensor(name: str, shape, kind: str, seed: int, device="cpu", dtype=torc
 def random_tensors(config, seed: int, device="cpu", dtype=torch.bfloat16) -> Iterator[Tuple[str, torch.Tensor]]:
     """(name, tensor) for every tensor the architecture's model expects."""
     entry = lookup_architecture(config.architecture)
-    spec = entry.build_spec(config)
+    spec = entry.spec_for(config)
     for name, (shape, kind) in spec.tensor_table().items():
         yield name, draw_tensor(name, shape, kind, seed, device, dtype)
 
