@@ -96,7 +96,7 @@ def write_safetensors(path, tensors: Iterable[Tuple[str, torch.Tensor]], metadat
             t = t.detach().cpu().contiguous()
             if t.dtype not in _NAMES:
                 raise SafetensorsError(f"tensor '{name}': dtype {t.dtype} cannot be stored")
-            raw = t.view(torch.uint8).numpy().tobytes() if t.numel() else b""
+            raw = t.reshape(-1).view(torch.uint8).numpy().tobytes() if t.numel() else b""     # reshape: a scalar has no axis to view
             header[name] = {"dtype": _NAMES[t.dtype], "shape": list(t.shape), "data_offsets": [offset, offset + len(raw)]}
             data.write(raw)
             offset += len(raw)
