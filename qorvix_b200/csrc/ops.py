@@ -5,6 +5,7 @@ library kernel; a missing or unbuildable library raises.
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
@@ -95,6 +96,7 @@ _ARGTYPES = {
     "qv_head_norm_gate": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _F, _I, _V],
     "qv_bias_attn_prepare": [_V, _I, _V, _I, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _V],
     "qv_bias_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _V, _I, _V, _V, _I, _F, _I, _V],
+    "qv_bias_attention_mma": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _V, _I, _V, _I, _F, _V, _I, _I, _V],
     "qv_argmax": [_V, _V, _I, _I, _L, _V],
     "qv_sample": [_V, _V, _I, _I, _L, _V, _V, _V, _V, _V, _V, _I, _V, _V, _V, _V],
 }
@@ -746,8 +748,73 @@ def bias_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, p
     _check(rc, "bias_attention_generic")
 
 
-def bias_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor) -> None:
-    """Attention with a distance bias for every token of the step (see bias_attention_generic)."""
+def bias_attention_table(bucket, bias):
+    """The bias per head and distance, times log2 e, for the tensor-core kernel: [H, len(bucket)] float32 from the
+    buckets of the distances (int32) and the table [rows, H]."""
+    return (bias.float()[bucket.long()] * math.log2(math.e)).t().contiguous()
+
+
+def bias_attention_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, G, n, dv, page, scale, table, gate, factor,
+                      slices: int = 1, slice_keys: int = 0) -> bool:
+    """Attention with a distance bias on the tensor cores (bfloat16; key and value sizes up to 128, multiples of 8) for S
+    segments that start at rows seg_q_start[s]; single tokens (max_q_len 1) share a tile among the query heads of a
+    key/value head, and slices > 1 cuts every token's keys into slices of slice_keys that a second launch joins.
+    table: bias_attention_table(...).  False, nothing written, for sizes it does not take."""
+    if q.dtype != torch.bfloat16 or n % 8 or dv % 8 or n > 128 or dv > 128 or q.stride(0) % 8 or out.stride(0) % 2:
+        return False
+    if max_q_len == 1 and H // G > 16:
+        return False
+    _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table, table, gate)
+    assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == cache_layer.dtype == torch.bfloat16
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (n + dv))
+    assert table.dtype == torch.float32 and table.is_contiguous() and table.shape[0] == H
+    assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
+    _i32(block_table, "block_table")
+    lib = _lib("bias_attention")
+    partial = None
+    if slices > 1:
+        assert max_q_len == 1
+        partial = torch.empty(S * H * slices * (2 + dv), device=q.device, dtype=torch.float32)
+    rc = lib.qv_bias_attention_mma(_ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(seg_q_start), _ptr(seg_pos0),
+                                   _ptr(block_table), block_table.shape[-1], S, max_q_len, H, G, n, dv, page, float(scale), _ptr(table),
+                                   table.shape[1] - 1, _ptr(gate), gate.stride(0) if gate is not None else 0, float(factor), _ptr(partial),
+                                   slices, slice_keys, _stream())
+    if rc == -2:
+        return False
+    _check(rc, "bias_attention_mma")
+    if slices > 1:
+        add_launches(1)                              # the kernel that joins the slices
+    return True
+
+
+def bias_attention_slices(tokens: int, G: int, max_ctx: int):
+    """(slices, keys a slice) for single query tokens, so that a step fills the SMs (a warp serves a token, a key/value
+    head and a slice): a function of the step's shape only (a captured step keeps it)."""
+    blocks = max(1, -(-max_ctx // 32))               # the kernel's blocks of keys
+    slices = max(1, min(4 * sm_count() // max(tokens * G, 1), -(-blocks // 2), 32))
+    return slices, -(-blocks // slices) * 32
+
+
+def bias_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor, table_of_distances=None) -> None:
+    """Attention with a distance bias for every token of the step (see bias_attention_generic).  bfloat16: the
+    tensor-core kernel where it takes the sizes and the table per distance is given (single tokens, which come first in a
+    step, with their keys in slices; portions with tiles of 64 rows); float32 and other sizes: the CUDA-core kernel."""
+    if q.dtype == torch.bfloat16 and table_of_distances is not None:
+        S = ctx.num_segments
+        n1 = 0                                        # leading segments of one token (decoded tokens)
+        while n1 < S and ctx.seg_len[n1] == 1:
+            n1 += 1
+        args = (H, G, n, dv, page, scale, table_of_distances)
+        ok = True
+        if n1:
+            slices, keys = bias_attention_slices(n1, G, ctx.max_ctx_len)
+            ok = bias_attention_tc(out, q, cache_layer, ctx.seg_q_start, ctx.seg_pos0, block_table, n1, 1, *args, gate, factor,
+                                   slices=slices, slice_keys=keys)
+        if ok and n1 < S:
+            ok = bias_attention_tc(out, q, cache_layer, ctx.seg_q_start[n1:], ctx.seg_pos0[n1:], block_table[n1:], S - n1,
+                                   max(ctx.seg_len[n1:]), *args, gate, factor)
+        if ok:
+            return
     bias_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor)
 
 

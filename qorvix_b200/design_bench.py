@@ -1,9 +1,9 @@
-"""Prefill and decode throughput of a Deganex or a Lotirax model at layer sizes that resemble real models, beside the
+"""Prefill and decode throughput of a Deganex, a Lotirax or a Tubazen model at layer sizes that resemble real models, beside the
 Llama decoder at equal width, depth and (active) feed-forward size, and the design's kernels alone with their roofline
 fractions beside the Llama kernels they correspond to.
 
-    python bench.py --design deganex|lotirax [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
-    python -m qorvix_b200.design_bench [--design lotirax]
+    python bench.py --design deganex|lotirax|tubazen [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
+    python -m qorvix_b200.design_bench [--design lotirax|tubazen]
 
 Random bfloat16 weights; timing with CUDA events after warm-up; kernels alone are timed in captured chains over
 buffers larger than L2 (kernel_bench.timed_chain).  Figures go out as one JSON line.
@@ -318,6 +318,136 @@ def run_lotirax(args, peaks) -> dict:
     return res
 
 
+# ------------------------------------------------------------------ Tubazen
+# Gated linear attention with eight heads of 128 key channels over 256 values; attention with a distance bias, 16 heads of
+# 128 on 4 key/value heads, beside a delta rule of 32 heads of 64; gated feed-forwards of 5,632.
+TUB_GLA = {"heads": 8, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 64}
+TUB_LEFT = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "bias_max": 4096, "bias_rows": 64,
+            "q_temp": {"coef": 0.2, "every": 512}}
+TUB_RIGHT = {"heads": 32, "dim": 64, "rank": 64}
+TUB_FF = {"kind": "dense", "ff": 5632}
+
+
+def tubazen_config(layers_per_kind: int) -> dict:
+    pair = {"type": "parallel", "mixer": {"left": TUB_LEFT, "right": TUB_RIGHT, "left_scale": 1.0, "right_scale": 1.0}, "mlp": TUB_FF}
+    layers = [{"type": "gla", "mixer": TUB_GLA, "mlp": TUB_FF}, pair] * layers_per_kind
+    return {"architecture": "Tubazen", "vocab": VOCAB, "width": WIDTH, "norm": {"eps": 1e-5}, "logit_scale": 1.0, "max_positions": 8192,
+            "layers": layers}
+
+
+def tubazen_llama_config(n_layers: int) -> dict:
+    return {"architectures": ["LlamaForCausalLM"], "vocab_size": VOCAB, "hidden_size": WIDTH, "intermediate_size": TUB_FF["ff"],
+            "num_hidden_layers": n_layers, "num_attention_heads": TUB_LEFT["heads"], "num_key_value_heads": TUB_LEFT["kv_heads"],
+            "head_dim": 128, "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": False}
+
+
+def bias_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
+    """Attention with a distance bias over the given segments, each ending at ctx_len cached tokens (the preparing kernel excluded)."""
+    from .parts.bias_attention import distance_buckets
+    a = TUB_LEFT
+    H, G, n, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+    S, T = len(seg_lens), sum(seg_lens)
+    blocks = -(-ctx_len // page)
+    width = G * (n + dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * ctx_len * width * 2)) + 1))
+    caches = torch.randn(copies, S * blocks + 1, page, width, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
+    ctx = _ctx(seg_lens, [ctx_len - m for m in seg_lens])
+    ctx.seg_len, ctx.seg_start_pos, ctx.max_ctx_len, ctx.captured = list(seg_lens), [ctx_len - m for m in seg_lens], ctx_len, False
+    ctx.seg_pos0 = torch.tensor(ctx.seg_start_pos, dtype=torch.int32, device="cuda")
+    q = torch.randn(T, H * n, device="cuda", dtype=torch.bfloat16)
+    gate = torch.randn(T, H * dv, device="cuda", dtype=torch.float32)
+    out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    rel = torch.randn(a["bias_rows"], H, device="cuda", dtype=torch.float32)
+    bucket = torch.from_numpy(distance_buckets(a["bias_rows"], a["bias_max"], 8192)).cuda()
+    bias = ops.bias_attention_table(bucket, rel)
+    us = kb.timed_chain(lambda i: ops.bias_attention(out, q, caches[i % copies], ctx, table, H, G, n, dv, page, a["scale"], bucket, rel, gate,
+                                                     1.0, table_of_distances=bias), launches=8)
+    pairs = sum(m * (ctx_len - m) + m * (m + 1) // 2 for m in seg_lens)
+    return kb._figures(us, S * ctx_len * width * 2 + (q.numel() + out.numel()) * 2 + gate.numel() * 4, H * pairs * (2.0 * n + 2.0 * dv), peaks)
+
+
+def bias_prepare_case(T, peaks, page=16) -> dict:
+    """Biases, the queries' temperature and the cache write of T tokens of one request."""
+    a = TUB_LEFT
+    H, G, n, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+    cols, width = (H + G) * n + G * dv, G * (n + dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (T * (cols * 4 + width * 2 + H * n * 2))) + 1))
+    projs = torch.randn(copies, T, cols, device="cuda", dtype=torch.float32)
+    blocks = -(-T // page)
+    caches = torch.zeros(copies, blocks + 1, page, width, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(blocks, dtype=torch.int32, device="cuda").view(1, blocks)
+    ctx = _ctx([T], [0])
+    bq, bk, bv = (torch.randn(m, device="cuda") for m in (H * n, G * n, G * dv))
+    q = torch.empty(copies, T, H * n, device="cuda", dtype=torch.bfloat16)
+    us = kb.timed_chain(lambda i: ops.bias_attn_prepare(q[i % copies], projs[i % copies], 0, H * n, (H + G) * n, bq, bk, bv, caches[i % copies], ctx,
+                                                        table, H, G, n, dv, page, 0.2, 512), launches=8)
+    return kb._figures(us, T * (cols * 4 + width * 2 + H * n * 2), 0.0, peaks)
+
+
+def channel_scan_case(kind, seg_lens, peaks) -> dict:
+    """The recurrence with a decay per key channel: gated linear attention ('gla') or the delta rule ('delta'), with the kernels that
+    form its decays (and unit keys) and the norm behind it."""
+    S, T = len(seg_lens), sum(seg_lens)
+    ctx = _ctx(seg_lens, [0] * S)
+    if kind == "gla":
+        H, dk, dv, R = TUB_GLA["heads"], TUB_GLA["dim"], TUB_GLA["vdim"], TUB_GLA["rank"]
+    else:
+        H, dk, dv, R = TUB_RIGHT["heads"], TUB_RIGHT["dim"], TUB_RIGHT["dim"], TUB_RIGHT["rank"]
+    n_state = ops.channel_scan_state_floats(H, dk, dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * n_state * 4)) + 1))
+    states = torch.zeros(copies, S, n_state, device="cuda", dtype=torch.float32)
+    f32 = dict(device="cuda", dtype=torch.float32)
+    q, k, a = (torch.randn(T, H * dk, **f32) * 0.1 for _ in range(3))
+    v, g = torch.randn(T, H * dv, **f32), torch.randn(T, H * dv, **f32)
+    low, w2, wb = torch.randn(T, R, **f32), torch.randn(H * dk, R, **f32) * 0.1, torch.randn(H * dk, **f32) + 3
+    nw = torch.ones(H * dv, **f32)
+    w, u, au = (torch.empty(T, H * dk, **f32) for _ in range(3))
+    y = torch.empty(T, H * dv, **f32)
+    out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
+
+    def run(i):
+        if kind == "gla":
+            ops.channel_gates(w, low, w2, wb, False, ops.GATE_POW_SIGMOID, 1.0 / 16.0)
+            ops.channel_scan(y, q, k, v, w, None, None, dk ** -0.5, states[i % copies], ctx, H, dk, dv)
+            ops.head_norm_gate(out, y, g, nw, H, 1e-5, ops.HEAD_GATE_SILU)
+        else:
+            ops.channel_gates(w, low, w2, wb, True, ops.GATE_EXP_NEG_SIGMOID, 0.6065)
+            ops.unit_keys(u, au, k, a, wb, H, dk, 1e-6)
+            ops.channel_scan(y, q, k, v, w, au, u, 1.0, states[i % copies], ctx, H, dk, dv)
+            ops.head_norm_gate(out, y, g, nw, H, 1e-5, ops.HEAD_GATE_SIGMOID)
+
+    us = kb.timed_chain(run, launches=6)
+    vecs = (3 if kind == "gla" else 4) * H * dk + 2 * H * dv
+    nbytes = 2 * S * n_state * 4 + T * vecs * 4 + T * H * dv * 2
+    return kb._figures(us, nbytes, (4.0 if kind == "gla" else 8.0) * T * H * dk * dv, peaks)
+
+
+def run_tubazen(args, peaks) -> dict:
+    n_layers = 2 * args.layers_per_kind
+    res = {"tubazen": model_throughput(tubazen_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
+           "llama_equal_size": model_throughput(tubazen_llama_config(n_layers), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup)}
+    T, B, C = args.prefill_tokens, args.batch, args.ctx
+    res["kernels"] = {
+        f"bias_attention_prefill_t{T}": bias_attention_case([T], T, peaks),
+        f"bias_attention_decode_b{B}_ctx{C}": bias_attention_case([1] * B, C, peaks),
+        f"bias_prepare_t{T}": bias_prepare_case(T, peaks), f"bias_prepare_t{B}": bias_prepare_case(B, peaks),
+        f"gla_scan_prefill_t{T}": channel_scan_case("gla", [T], peaks), f"gla_scan_decode_b{B}": channel_scan_case("gla", [1] * B, peaks),
+        f"delta_scan_prefill_t{T}": channel_scan_case("delta", [T], peaks), f"delta_scan_decode_b{B}": channel_scan_case("delta", [1] * B, peaks),
+    }
+    # the like kernels of the other designs: the differential attention and the recurrences with one decay a head
+    res["like_kernels"] = {
+        f"diff_attention_prefill_t{T}": diff_attention_case([T], T, peaks), f"diff_attention_decode_b{B}_ctx{C}": diff_attention_case([1] * B, C, peaks),
+        f"mlstm_scan_prefill_t{T}": scan_case("mlstm", [T], peaks), f"mlstm_scan_decode_b{B}": scan_case("mlstm", [1] * B, peaks),
+        f"mamba2_scan_prefill_t{T}": scan_case("mamba2", [T], peaks), f"mamba2_scan_decode_b{B}": scan_case("mamba2", [1] * B, peaks),
+    }
+    from .config import LlamaConfig
+    like = kb.headline_kernels(LlamaConfig.from_dict(tubazen_llama_config(n_layers)), B, C, T, peaks)
+    ops.check_kernel_errors()
+    res["llama_kernels"] = {k: v for k, v in like.items() if "attention" in k or "gate_up" in k or "down" in k}
+    return res
+
+
 def run(args, peaks) -> dict:
     n_layers = 3 * args.layers_per_kind
     res = {"deganex": model_throughput(deganex_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
@@ -340,7 +470,7 @@ def run(args, peaks) -> dict:
 
 def main(argv=None, peaks=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--design", default="deganex", choices=["deganex", "lotirax"])
+    ap.add_argument("--design", default="deganex", choices=["deganex", "lotirax", "tubazen"])
     ap.add_argument("--layers-per-kind", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1024)
@@ -351,6 +481,8 @@ def main(argv=None, peaks=None) -> int:
     peaks = peaks or {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
     if args.design == "lotirax":
         res, model = run_lotirax(args, peaks), f"Lotirax, width {WIDTH}, 4 layers of which 2 run twice"
+    elif args.design == "tubazen":
+        res, model = run_tubazen(args, peaks), f"Tubazen, width {WIDTH}, {2 * args.layers_per_kind} layers"
     else:
         res, model = run(args, peaks), f"Deganex, width {WIDTH}, {3 * args.layers_per_kind} layers"
     d = res[args.design]

@@ -47,6 +47,8 @@ class BiasedAttention(SharedIOMixer):
         self.out_cols = self.H * self.dv
         self.rel = source.get(spec.rel_bias, dtype=torch.float32)                                  # [rows, heads]
         self.bucket = torch.from_numpy(distance_buckets(spec.bias_rows, spec.bias_max, rt.max_positions)).to(rt.device)
+        # the tensor-core kernel reads the bias per (head, distance)
+        self.table = ops.bias_attention_table(self.bucket, self.rel) if rt.dtype == torch.bfloat16 else None
 
     def cache_spec(self):
         return PagedRowsSpec(self.G * (self.n + self.dv), 0)
@@ -72,7 +74,7 @@ class BiasedAttention(SharedIOMixer):
         ops.bias_attn_prepare(q, proj, 0, k_off, v_off, self.bq, self.bk, self.bv, cache.tensor, ctx, bt, H, G, n, dv, cache.page_size,
                               s.temp_coef, s.temp_every)
         ops.bias_attention(out, q, cache.tensor, ctx, bt, H, G, n, dv, cache.page_size, s.scale, self.bucket, self.rel,
-                           proj[:, g_off: g_off + H * dv], factor)
+                           proj[:, g_off: g_off + H * dv], factor, table_of_distances=self.table)
 
 
 register_part("mixer", "biased_attention", BiasedAttention)
