@@ -402,13 +402,16 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
         bt_split3(sc[2 * kk + 1][0], sc[2 * kk + 1][1], t[0][2], t[1][2], t[2][2]);
         bt_split3(sc[2 * kk + 1][2], sc[2 * kk + 1][3], t[0][3], t[1][3], t[2][3]);
 #pragma unroll
-        for (int np = 0; np < DP / 16; ++np) {
-          uint32_t b0, b1, b2, b3;
-          bt_ldmatrix4_trans(b0, b1, b2, b3, tV + (kk * 16 + (mat & 1) * 8 + r8) * VS + (np * 2 + (mat >> 1)) * 8);
+        for (int np = 0; np < DP / 16; np += 2) {          // four accumulators in turn: no product waits for the one before it
+          uint32_t b[8];
+          bt_ldmatrix4_trans(b[0], b[1], b[2], b[3], tV + (kk * 16 + (mat & 1) * 8 + r8) * VS + (np * 2 + (mat >> 1)) * 8);
+          bt_ldmatrix4_trans(b[4], b[5], b[6], b[7], tV + (kk * 16 + (mat & 1) * 8 + r8) * VS + (np * 2 + 2 + (mat >> 1)) * 8);
 #pragma unroll
           for (int term = 2; term >= 0; --term) {          // the small terms first
-            bt_mma(o[2 * np], t[term], b0, b1);
-            bt_mma(o[2 * np + 1], t[term], b2, b3);
+            bt_mma(o[2 * np], t[term], b[0], b[1]);
+            bt_mma(o[2 * np + 1], t[term], b[2], b[3]);
+            bt_mma(o[2 * np + 2], t[term], b[4], b[5]);
+            bt_mma(o[2 * np + 3], t[term], b[6], b[7]);
           }
         }
       }

@@ -10,10 +10,10 @@
 //                       EXP_NEG_SIGMOID  exp(-p * sigmoid(z))          (a decay bounded below by exp(-p))
 //                     f the identity or tanh.
 // qv_unit_keys        u = k / sqrt(sum(k^2) + eps) per head and au = sigmoid(a + bias) * u.
-// qv_channel_scan     the recurrence.  The columns of S are independent of one another, so a warp owns C of them, its lanes
-//                     owning the rows (row = lane + 32 i): u^T S and S^T q are sums over a warp (shuffles, a fixed order), and
-//                     warps never wait for one another.  Only u^T S lies on the chain from token to token; the next token's
-//                     vectors are fetched while the present one is worked on.
+// qv_channel_scan     the recurrence.  The columns of S are independent of one another: a few lanes own a column, each a run of
+//                     its rows in registers, so u^T S and S^T q are short sums in a fixed order; the warps of a CTA share the
+//                     tokens' vectors, which arrive in shared memory by cp.async a chunk ahead.  Only u^T S lies on the chain
+//                     from token to token.
 // qv_head_norm_gate   the unit norm per head (RMS over a head's values) with weight, gate (sigmoid or SiLU, behind the norm)
 //                     and a fixed factor that follows a scan.
 //
@@ -25,46 +25,66 @@
 #define GATE_POW_SIGMOID 0
 #define GATE_EXP_NEG_SIGMOID 1
 
-// x1 [T, R] (row stride ld_x), W2 [N, R] float32, bias [N] or null -> out [T, N] (row stride ld_out)
+// x1 [T, R] (row stride ld_x), W2 transposed [R, N] float32, bias [N] or null -> out [T, N] (row stride ld_out).
+// A CTA takes CG_TOKENS tokens, so that an entry of W2 is read once for all of them; a sum runs over r ascending.
+#define CG_TOKENS 8
 __global__ void __launch_bounds__(256) channel_gates_kernel(float* __restrict__ out, int ld_out, const float* __restrict__ x1, int ld_x,
-                                                           const float* __restrict__ w2, const float* __restrict__ bias, int N, int R,
-                                                           int pre_tanh, int kind, float p) {
-  extern __shared__ float xs[];                    // R floats: the token's low-rank row
+                                                           const float* __restrict__ w2t, const float* __restrict__ bias, int T, int N,
+                                                           int R, int pre_tanh, int kind, float p) {
+  extern __shared__ float xs[];                    // [CG_TOKENS][R]: the tokens' low-rank rows
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
-  for (int r = threadIdx.x; r < R; r += blockDim.x) {
-    const float v = x1[(size_t)t * ld_x + r];
-    xs[r] = pre_tanh ? tanhf(v) : v;
+  const int t0 = blockIdx.x * CG_TOKENS;
+  const int nt = min(CG_TOKENS, T - t0);
+  for (int i = threadIdx.x; i < CG_TOKENS * R; i += blockDim.x) {
+    const int j = i / R, r = i % R;
+    float v = 0.f;
+    if (j < nt) {
+      v = x1[(size_t)(t0 + j) * ld_x + r];
+      if (pre_tanh) v = tanhf(v);
+    }
+    xs[i] = v;
   }
   __syncthreads();
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < N; c += gridDim.y * blockDim.x) {
-    const float* wr = w2 + (size_t)c * R;
-    float z = 0.f;
-    for (int r = 0; r < R; ++r) z = fmaf(xs[r], wr[r], z);
-    if (bias) z += bias[c];
-    float g;
-    if (kind == GATE_POW_SIGMOID) {
-      const float ls = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));          // log sigmoid(z)
-      g = expf(p * ls);
-    } else {
-      g = expf(-p * (1.0f / (1.0f + expf(-z))));
+    float z[CG_TOKENS];
+#pragma unroll
+    for (int j = 0; j < CG_TOKENS; ++j) z[j] = 0.f;
+#pragma unroll 8
+    for (int r = 0; r < R; ++r) {
+      const float wv = w2t[(size_t)r * N + c];
+#pragma unroll
+      for (int j = 0; j < CG_TOKENS; ++j) z[j] = fmaf(xs[j * R + r], wv, z[j]);
     }
-    out[(size_t)t * ld_out + c] = g;
+    const float bc = bias ? bias[c] : 0.f;
+#pragma unroll
+    for (int j = 0; j < CG_TOKENS; ++j) {
+      if (j >= nt) break;
+      const float zz = z[j] + bc;
+      float g;
+      if (kind == GATE_POW_SIGMOID) {
+        const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));          // log sigmoid(z)
+        g = expf(p * ls);
+      } else {
+        g = expf(-p * (1.0f / (1.0f + expf(-zz))));
+      }
+      out[(size_t)(t0 + j) * ld_out + c] = g;
+    }
   }
 }
 
-extern "C" int qv_channel_gates(float* out, int ld_out, const float* x1, int ld_x, const float* w2, const float* bias, int T, int N,
+extern "C" int qv_channel_gates(float* out, int ld_out, const float* x1, int ld_x, const float* w2t, const float* bias, int T, int N,
                                 int R, int pre_tanh, int kind, float p, void* stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (R <= 0 || (size_t)R * sizeof(float) > 48 * 1024) return QV_ERR_UNSUPPORTED;
+  if (R <= 0 || (size_t)CG_TOKENS * R * sizeof(float) > 48 * 1024) return QV_ERR_UNSUPPORTED;
   if (kind != GATE_POW_SIGMOID && kind != GATE_EXP_NEG_SIGMOID) return QV_ERR_UNSUPPORTED;
   const int by = (N + 255) / 256 < 64 ? (N + 255) / 256 : 64;
   cudaStream_t st = (cudaStream_t)stream;
-  for (int done = 0; done < T; done += 65535) {
-    const int rows = T - done < 65535 ? T - done : 65535;
-    const int rc = qv_launch(channel_gates_kernel, dim3(rows, by), dim3(256), (size_t)R * sizeof(float), st,
-                             out + (size_t)done * ld_out, ld_out, x1 + (size_t)done * ld_x, ld_x, w2, bias, N, R, pre_tanh, kind, p);
+  const int per = 65535 * CG_TOKENS;
+  for (int done = 0; done < T; done += per) {
+    const int rows = T - done < per ? T - done : per;
+    const int rc = qv_launch(channel_gates_kernel, dim3((rows + CG_TOKENS - 1) / CG_TOKENS, by), dim3(256), (size_t)CG_TOKENS * R * sizeof(float),
+                             st, out + (size_t)done * ld_out, ld_out, x1 + (size_t)done * ld_x, ld_x, w2t, bias, rows, N, R, pre_tanh, kind, p);
     if (rc) return rc;
   }
   return 0;
@@ -108,8 +128,16 @@ extern "C" int qv_unit_keys(float* u, float* au, const float* k, int ld_k, const
 }
 
 // ---------------------------------------------------------------- the scan
+// A column of S belongs to LPC lanes that hold CS_ROWS rows each (rows lic * CS_ROWS ..), so LPC = 1, 2, 4, 8, 16 serves key
+// sizes up to 16, 32, 64, 128, 256; a warp holds 32 / LPC columns, a CTA four times that.  (Eight rows a lane and the next
+// token's vectors fetched into registers ahead were measured and were slower: more shuffles and more registers.)  The sums over a column's rows
+// are CS_ROWS multiply-adds a lane (four partial sums, a fixed order) and log2(LPC) shuffles.  The tokens' vectors arrive in
+// shared memory by cp.async, a chunk of tokens ahead of the warps that work through them, and are read 16 bytes at a time.
+// The state of a request is kept in the order of the registers ([head][warp tile][row of the lane][lane]), so that it is read and
+// written in whole lines; rows and columns beyond the sizes hold zeros.
 #define CS_WARPS 4
-#define CS_COLS 4           // value columns a warp owns
+#define CS_ROWS 16
+#define CS_PAD 20           // floats a lane's rows take in a stage: 16 and 4 of padding, so that 16-byte reads of the LPC lanes miss one another's banks
 
 struct ChannelScanArgs {
   float* out; int ld_out;                 // [T, H * dv]
@@ -120,111 +148,144 @@ struct ChannelScanArgs {
   const float* au; int ld_au;             // removal: a * u and u, or null
   const float* u; int ld_u;
   float q_scale;
-  float* state; long long slot_stride;    // per slot: [H][dv][dk]
+  float* state; long long slot_stride;    // per slot: [H][tiles][CS_ROWS][32]
   const int* seg_q_start; const int* seg_slot;
   int H, dk, dv;
 };
 
-template <int RPL, bool REMOVAL>
-__global__ void __launch_bounds__(32 * CS_WARPS) channel_scan_kernel(ChannelScanArgs a) {
+// 4 or 16 bytes, or as many zero bytes where `valid` is false
+__device__ __forceinline__ void cs_cp4(float* dst, const float* src, bool valid) {
+  const int bytes = valid ? 4 : 0;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cs_cp16(float* dst, const float* src, bool valid) {
+  const int bytes = valid ? 16 : 0;
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((unsigned)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ float cs_sum4(const float* p) { return (p[0] + p[1]) + (p[2] + p[3]); }
+
+// `chunk` tokens a stage, two stages.  vec4: every vector starts on 16 bytes and dk is a multiple of 4 (16-byte copies).
+template <int LPC, bool REMOVAL>
+__global__ void __launch_bounds__(32 * CS_WARPS) channel_scan_kernel(ChannelScanArgs a, int chunk, int vec4) {
+  extern __shared__ __align__(16) float cs_ring[];
+  constexpr int NV = REMOVAL ? 5 : 3;
+  constexpr int CPW = 32 / LPC, CTA_COLS = CS_WARPS * CPW, NTH = 32 * CS_WARPS;
+  constexpr int VEC = CS_PAD * LPC;                // floats a vector takes in a stage
+  constexpr int ROW = NV * VEC + CTA_COLS;         // floats a token takes
   pdl_wait();
   pdl_launch_dependents();
   const int s = blockIdx.x, h = blockIdx.y;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lic = lane % LPC, cw = lane / LPC;
   const int dk = a.dk, dv = a.dv;
-  const int col0 = (blockIdx.z * CS_WARPS + warp) * CS_COLS;
-  if (col0 >= dv) return;                          // warps are on their own: nothing waits for this one
+  const int cta_col0 = blockIdx.z * CTA_COLS;
+  const int col = cta_col0 + warp * CPW + cw;
+  const int tiles = (dv + CPW - 1) / CPW;
   const int q0 = a.seg_q_start[s], len = a.seg_q_start[s + 1] - q0;
-  float* st = a.state + (size_t)a.seg_slot[s] * a.slot_stride + ((size_t)h * dv + col0) * dk;
-  float S[CS_COLS][RPL];
+  const int tile = blockIdx.z * CS_WARPS + warp;
+  const bool active = tile < tiles;
+  float* st = a.state + (size_t)a.seg_slot[s] * a.slot_stride + ((size_t)h * tiles + tile) * (CS_ROWS * 32) + lane;
+  float S[CS_ROWS];
 #pragma unroll
-  for (int c = 0; c < CS_COLS; ++c)
+  for (int i = 0; i < CS_ROWS; ++i) S[i] = active ? st[i * 32] : 0.f;
+  const size_t hk = (size_t)h * dk, hv = (size_t)h * dv;
+  const float* srcs[5] = {a.w + hk, a.k + hk, a.q + hk, REMOVAL ? a.au + hk : nullptr, REMOVAL ? a.u + hk : nullptr};
+  const int lds[5] = {a.ld_w, a.ld_k, a.ld_q, a.ld_au, a.ld_u};
+  auto issue = [&](int c) {
+    float* base = cs_ring + (size_t)(c & 1) * chunk * ROW;
+    const int j0 = c * chunk, nt = min(chunk, len - j0);
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const int r = lane + 32 * i;
-      S[c][i] = (r < dk && col0 + c < dv) ? st[(size_t)c * dk + r] : 0.f;
-    }
-  const size_t hk = (size_t)h * dk, hv = (size_t)h * dv + col0;
-  float wn[RPL], kn[RPL], qn[RPL], aun[RPL], un[RPL], vn[CS_COLS];
-  auto fetch = [&](int j) {
-    const size_t t = (size_t)(q0 + j);
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const int r = lane + 32 * i;
-      const bool ok = r < dk;
-      wn[i] = ok ? a.w[t * a.ld_w + hk + r] : 0.f;
-      kn[i] = ok ? a.k[t * a.ld_k + hk + r] : 0.f;
-      qn[i] = ok ? a.q[t * a.ld_q + hk + r] : 0.f;
-      if (REMOVAL) {
-        aun[i] = ok ? a.au[t * a.ld_au + hk + r] : 0.f;
-        un[i] = ok ? a.u[t * a.ld_u + hk + r] : 0.f;
+    for (int v = 0; v < NV; ++v) {
+      if (vec4) {
+        constexpr int PER = CS_ROWS * LPC / 4;       // 16-byte pieces a vector (padding rows included)
+        for (int i = tid; i < nt * PER; i += NTH) {
+          const int j = i / PER, r = (i % PER) * 4;
+          cs_cp16(base + j * ROW + v * VEC + r + (r / CS_ROWS) * (CS_PAD - CS_ROWS), srcs[v] + (size_t)(q0 + j0 + j) * lds[v] + r, r < dk);
+        }
+      } else {
+        constexpr int PER = CS_ROWS * LPC;
+        for (int i = tid; i < nt * PER; i += NTH) {
+          const int j = i / PER, r = i % PER;
+          cs_cp4(base + j * ROW + v * VEC + r + (r / CS_ROWS) * (CS_PAD - CS_ROWS), srcs[v] + (size_t)(q0 + j0 + j) * lds[v] + r, r < dk);
+        }
       }
     }
-#pragma unroll
-    for (int c = 0; c < CS_COLS; ++c) vn[c] = col0 + c < dv ? a.v[t * a.ld_v + hv + c] : 0.f;
+    for (int i = tid; i < nt * CTA_COLS; i += NTH) {
+      const int j = i / CTA_COLS, cc = i % CTA_COLS;
+      cs_cp4(base + j * ROW + NV * VEC + cc, a.v + (size_t)(q0 + j0 + j) * a.ld_v + hv + cta_col0 + cc, cta_col0 + cc < dv);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
   };
-  if (len > 0) fetch(0);
-  for (int j = 0; j < len; ++j) {
-    float wc[RPL], kc[RPL], qc[RPL], auc[RPL], uc[RPL], vc[CS_COLS];
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      wc[i] = wn[i]; kc[i] = kn[i]; qc[i] = qn[i];
-      if (REMOVAL) { auc[i] = aun[i]; uc[i] = un[i]; }
+  const int nchunks = (len + chunk - 1) / chunk;
+  if (nchunks > 0) issue(0);
+  for (int c = 0; c < nchunks; ++c) {
+    if (c + 1 < nchunks) {
+      issue(c + 1);
+      asm volatile("cp.async.wait_group 1;" ::: "memory");
+    } else {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
+    __syncthreads();
+    const int j0 = c * chunk, nt = min(chunk, len - j0);
+    if (active) {
+      for (int j = 0; j < nt; ++j) {
+        const float* d = cs_ring + ((size_t)(c & 1) * chunk + j) * ROW;
+        const float4* pw = (const float4*)(d + lic * CS_PAD);
+        const float4* pk = (const float4*)(d + VEC + lic * CS_PAD);
+        const float4* pq = (const float4*)(d + 2 * VEC + lic * CS_PAD);
+        const float vv = d[NV * VEC + warp * CPW + cw];
+        float dd = 0.f;
+        if (REMOVAL) {
+          const float4* pu = (const float4*)(d + 4 * VEC + lic * CS_PAD);
+          float p[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-    for (int c = 0; c < CS_COLS; ++c) vc[c] = vn[c];
-    if (j + 1 < len) fetch(j + 1);
-    float d[CS_COLS];
-    if (REMOVAL) {
+          for (int i = 0; i < CS_ROWS / 4; ++i) {
+            const float4 u4 = pu[i];
+            p[0] = fmaf(u4.x, S[4 * i], p[0]); p[1] = fmaf(u4.y, S[4 * i + 1], p[1]);
+            p[2] = fmaf(u4.z, S[4 * i + 2], p[2]); p[3] = fmaf(u4.w, S[4 * i + 3], p[3]);
+          }
+          dd = cs_sum4(p);
 #pragma unroll
-      for (int c = 0; c < CS_COLS; ++c) {
-        float p = 0.f;
+          for (int o = LPC / 2; o > 0; o >>= 1) dd += __shfl_xor_sync(0xffffffffu, dd, o);
+        }
+        float y[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int i = 0; i < RPL; ++i) p = fmaf(uc[i], S[c][i], p);
-        d[c] = p;
+        for (int i = 0; i < CS_ROWS / 4; ++i) {
+          const float4 w4 = pw[i], k4 = pk[i], q4 = pq[i];
+          float n0 = fmaf(k4.x, vv, w4.x * S[4 * i]), n1 = fmaf(k4.y, vv, w4.y * S[4 * i + 1]);
+          float n2 = fmaf(k4.z, vv, w4.z * S[4 * i + 2]), n3 = fmaf(k4.w, vv, w4.w * S[4 * i + 3]);
+          if (REMOVAL) {
+            const float4 a4 = ((const float4*)(d + 3 * VEC + lic * CS_PAD))[i];
+            n0 = fmaf(-a4.x, dd, n0); n1 = fmaf(-a4.y, dd, n1); n2 = fmaf(-a4.z, dd, n2); n3 = fmaf(-a4.w, dd, n3);
+          }
+          S[4 * i] = n0; S[4 * i + 1] = n1; S[4 * i + 2] = n2; S[4 * i + 3] = n3;
+          y[0] = fmaf(q4.x, n0, y[0]); y[1] = fmaf(q4.y, n1, y[1]); y[2] = fmaf(q4.z, n2, y[2]); y[3] = fmaf(q4.w, n3, y[3]);
+        }
+        float yy = cs_sum4(y);
+#pragma unroll
+        for (int o = LPC / 2; o > 0; o >>= 1) yy += __shfl_xor_sync(0xffffffffu, yy, o);
+        if (lic == 0 && col < dv) a.out[(size_t)(q0 + j0 + j) * a.ld_out + hv + col] = yy * a.q_scale;
       }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int c = 0; c < CS_COLS; ++c) d[c] += __shfl_xor_sync(0xffffffffu, d[c], o);
     }
-    float y[CS_COLS];
-#pragma unroll
-    for (int c = 0; c < CS_COLS; ++c) {
-      float p = 0.f;
-#pragma unroll
-      for (int i = 0; i < RPL; ++i) {
-        float nv = fmaf(kc[i], vc[c], wc[i] * S[c][i]);
-        if (REMOVAL) nv = fmaf(-auc[i], d[c], nv);
-        S[c][i] = nv;
-        p = fmaf(qc[i], nv, p);
-      }
-      y[c] = p;
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-      for (int c = 0; c < CS_COLS; ++c) y[c] += __shfl_xor_sync(0xffffffffu, y[c], o);
-    float mine = y[0];
-#pragma unroll
-    for (int c = 1; c < CS_COLS; ++c) if (lane == c) mine = y[c];
-    if (lane < CS_COLS && col0 + lane < dv) a.out[(size_t)(q0 + j) * a.ld_out + hv + lane] = mine * a.q_scale;
+    __syncthreads();
   }
+  if (!active) return;
 #pragma unroll
-  for (int c = 0; c < CS_COLS; ++c)
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const int r = lane + 32 * i;
-      if (r < dk && col0 + c < dv) st[(size_t)c * dk + r] = S[c][i];
-    }
+  for (int i = 0; i < CS_ROWS; ++i) st[i * 32] = S[i];
 }
 
-extern "C" long long qv_channel_scan_state_floats(int H, int dk, int dv) { return (long long)H * dk * dv; }
+static inline int cs_lanes_per_column(int dk) { return dk <= 16 ? 1 : dk <= 32 ? 2 : dk <= 64 ? 4 : dk <= 128 ? 8 : 16; }
 
+extern "C" long long qv_channel_scan_state_floats(int H, int dk, int dv) {
+  const int cpw = 32 / cs_lanes_per_column(dk);
+  return (long long)H * ((dv + cpw - 1) / cpw) * CS_ROWS * 32;
+}
+
+// max_q_len: the longest segment of the step (how many tokens a stage of the ring holds follows from it).
 extern "C" int qv_channel_scan(float* out, int ld_out, const float* q, int ld_q, const float* k, int ld_k, const float* v, int ld_v,
                                const float* w, int ld_w, const float* au, int ld_au, const float* u, int ld_u, float q_scale,
-                               float* state, long long slot_stride, const int* seg_q_start, const int* seg_slot, int S, int H, int dk,
-                               int dv, void* stream) {
+                               float* state, long long slot_stride, const int* seg_q_start, const int* seg_slot, int S, int max_q_len,
+                               int H, int dk, int dv, void* stream) {
   if (S <= 0) return 0;
   if (H <= 0 || dk <= 0 || dv <= 0 || H > 65535 || (au == nullptr) != (u == nullptr)) return QV_ERR_UNSUPPORTED;
   if (dk > 256) return QV_ERR_TOO_LARGE;
@@ -232,21 +293,33 @@ extern "C" int qv_channel_scan(float* out, int ld_out, const float* q, int ld_q,
   a.out = out; a.ld_out = ld_out; a.q = q; a.ld_q = ld_q; a.k = k; a.ld_k = ld_k; a.v = v; a.ld_v = ld_v; a.w = w; a.ld_w = ld_w;
   a.au = au; a.ld_au = ld_au; a.u = u; a.ld_u = ld_u; a.q_scale = q_scale; a.state = state; a.slot_stride = slot_stride;
   a.seg_q_start = seg_q_start; a.seg_slot = seg_slot; a.H = H; a.dk = dk; a.dv = dv;
-  const int per_cta = CS_WARPS * CS_COLS;
-  const int tiles = (dv + per_cta - 1) / per_cta;
-  if (tiles > 65535) return QV_ERR_TOO_LARGE;
-  dim3 grid(S, H, tiles), block(32 * CS_WARPS);
+  const int lpc = cs_lanes_per_column(dk);
+  const int cta_cols = CS_WARPS * 32 / lpc;
+  const int ctas = (dv + cta_cols - 1) / cta_cols;
+  if (ctas > 65535) return QV_ERR_TOO_LARGE;
+  dim3 grid(S, H, ctas), block(32 * CS_WARPS);
   cudaStream_t st = (cudaStream_t)stream;
   const bool rem = au != nullptr;
-#define CS_LAUNCH(RPL)                                                                   \
-  do {                                                                                   \
-    if (rem) return qv_launch(channel_scan_kernel<RPL, true>, grid, block, 0, st, a);    \
-    return qv_launch(channel_scan_kernel<RPL, false>, grid, block, 0, st, a);            \
+  const int row = (rem ? 5 : 3) * CS_PAD * lpc + cta_cols;
+  int chunk = max_q_len < 1 ? 1 : (max_q_len > 16 ? 16 : max_q_len);
+  while (chunk > 1 && (size_t)2 * chunk * row * sizeof(float) > 64 * 1024) chunk >>= 1;
+  const size_t smem = (size_t)2 * chunk * row * sizeof(float);
+  auto aligned = [](const float* p, int ld) { return p == nullptr || (((uintptr_t)p & 15) == 0 && ld % 4 == 0); };
+  const int vec4 = dk % 4 == 0 && aligned(q, ld_q) && aligned(k, ld_k) && aligned(w, ld_w) && aligned(au, ld_au) && aligned(u, ld_u);
+#define CS_LAUNCH(LPC_)                                                                                                  \
+  do {                                                                                                                   \
+    if (rem) {                                                                                                           \
+      cudaFuncSetAttribute(channel_scan_kernel<LPC_, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);     \
+      return qv_launch(channel_scan_kernel<LPC_, true>, grid, block, smem, st, a, chunk, vec4);                          \
+    }                                                                                                                    \
+    cudaFuncSetAttribute(channel_scan_kernel<LPC_, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024);      \
+    return qv_launch(channel_scan_kernel<LPC_, false>, grid, block, smem, st, a, chunk, vec4);                           \
   } while (0)
-  if (dk <= 32) CS_LAUNCH(1);
-  if (dk <= 64) CS_LAUNCH(2);
-  if (dk <= 128) CS_LAUNCH(4);
-  CS_LAUNCH(8);
+  if (lpc == 1) CS_LAUNCH(1);
+  if (lpc == 2) CS_LAUNCH(2);
+  if (lpc == 4) CS_LAUNCH(4);
+  if (lpc == 8) CS_LAUNCH(8);
+  CS_LAUNCH(16);
 #undef CS_LAUNCH
 }
 

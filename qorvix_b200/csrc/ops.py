@@ -92,7 +92,7 @@ _ARGTYPES = {
     "qv_channel_gates": [_V, _I, _V, _I, _V, _V, _I, _I, _I, _I, _I, _F, _V],
     "qv_unit_keys": [_V, _V, _V, _I, _V, _I, _V, _I, _I, _I, _F, _V],
     "qv_channel_scan_state_floats": [_I, _I, _I],
-    "qv_channel_scan": [_V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _F, _V, _L, _V, _V, _I, _I, _I, _I, _V],
+    "qv_channel_scan": [_V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
     "qv_head_norm_gate": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _F, _I, _V],
     "qv_bias_attn_prepare": [_V, _I, _V, _I, _I, _I, _I, _V, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _V],
     "qv_bias_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _F, _V, _I, _V, _V, _I, _F, _I, _V],
@@ -653,16 +653,16 @@ GATE_POW_SIGMOID, GATE_EXP_NEG_SIGMOID = 0, 1
 HEAD_GATE_SIGMOID, HEAD_GATE_SILU = 0, 1
 
 
-def channel_gates(out, x1, w2, bias, pre_tanh: bool, kind: int, p: float) -> None:
-    """out[t, c] (float32) = g(sum_r f(x1[t, r]) w2[c, r] + bias[c]): f the identity or tanh; g(z) = sigmoid(z)^p
+def channel_gates(out, x1, w2t, bias, pre_tanh: bool, kind: int, p: float) -> None:
+    """out[t, c] (float32) = g(sum_r f(x1[t, r]) w2t[r, c] + bias[c]): f the identity or tanh; g(z) = sigmoid(z)^p
     (GATE_POW_SIGMOID) or exp(-p sigmoid(z)) (GATE_EXP_NEG_SIGMOID).  x1 float32 [T, R] (a column slice is fine),
-    w2 float32 [N, R]."""
-    _need_cuda(out, x1, w2, bias)
+    w2t float32 [R, N]: the up matrix transposed, so that neighbouring channels lie side by side."""
+    _need_cuda(out, x1, w2t, bias)
     T, R = x1.shape
-    N = w2.shape[0]
-    assert out.dtype == x1.dtype == w2.dtype == torch.float32 and out.stride(1) == 1 and x1.stride(1) == 1 and w2.is_contiguous()
-    assert tuple(out.shape) == (T, N) and w2.shape[1] == R and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))
-    rc = _lib("channel_scan").qv_channel_gates(_ptr(out), out.stride(0), _ptr(x1), x1.stride(0), _ptr(w2), _ptr(bias), T, N, R,
+    N = w2t.shape[1]
+    assert out.dtype == x1.dtype == w2t.dtype == torch.float32 and out.stride(1) == 1 and x1.stride(1) == 1 and w2t.is_contiguous()
+    assert tuple(out.shape) == (T, N) and w2t.shape[0] == R and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))
+    rc = _lib("channel_scan").qv_channel_gates(_ptr(out), out.stride(0), _ptr(x1), x1.stride(0), _ptr(w2t), _ptr(bias), T, N, R,
                                                1 if pre_tanh else 0, kind, float(p), _stream())
     _check(rc, "channel_gates")
 
@@ -692,11 +692,11 @@ def channel_scan(out, q, k, v, w, au, u, q_scale: float, state, ctx, H: int, dk:
     _need_cuda(out, q, k, v, w, au, u, state)
     for x in (out, q, k, v, w, au, u):
         assert x is None or (x.dtype == torch.float32 and x.stride(1) == 1)
-    assert state.dtype == torch.float32 and state.stride(-1) == 1 and state.shape[-1] >= H * dk * dv
+    assert state.dtype == torch.float32 and state.stride(-1) == 1 and state.shape[-1] >= channel_scan_state_floats(H, dk, dv)
     rc = _lib("channel_scan").qv_channel_scan(
         _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(v), v.stride(0), _ptr(w), w.stride(0), _ptr(au),
         au.stride(0) if au is not None else 0, _ptr(u), u.stride(0) if u is not None else 0, float(q_scale), _ptr(state),
-        state.stride(0), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), ctx.num_segments, H, dk, dv, _stream())
+        state.stride(0), _ptr(ctx.seg_q_start), _ptr(ctx.seg_slot), ctx.num_segments, int(ctx.max_q_len), H, dk, dv, _stream())
     _check(rc, "channel_scan")
 
 

@@ -400,7 +400,7 @@ def channel_scan_case(kind, seg_lens, peaks) -> dict:
     f32 = dict(device="cuda", dtype=torch.float32)
     q, k, a = (torch.randn(T, H * dk, **f32) * 0.1 for _ in range(3))
     v, g = torch.randn(T, H * dv, **f32), torch.randn(T, H * dv, **f32)
-    low, w2, wb = torch.randn(T, R, **f32), torch.randn(H * dk, R, **f32) * 0.1, torch.randn(H * dk, **f32) + 3
+    low, w2, wb = torch.randn(T, R, **f32), torch.randn(R, H * dk, **f32) * 0.1, torch.randn(H * dk, **f32) + 3
     nw = torch.ones(H * dv, **f32)
     w, u, au = (torch.empty(T, H * dk, **f32) for _ in range(3))
     y = torch.empty(T, H * dv, **f32)

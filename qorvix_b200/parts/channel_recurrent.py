@@ -27,11 +27,11 @@ class _ChannelDecay:
         self.inner_tanh = bool(spec.inner_tanh)
         self.rank = int(spec.rank)
         self.down = source.get(spec.down)
-        self.up = source.get(spec.up, dtype=torch.float32)           # small: float32 on every path
+        self.up = source.get(spec.up, dtype=torch.float32).t().contiguous()     # [rank, channels]; small: float32 on every path
         self.bias = source.get(spec.bias, dtype=torch.float32)
 
     def apply(self, low_rank):
-        out = torch.empty((low_rank.shape[0], self.up.shape[0]), device=low_rank.device, dtype=torch.float32)
+        out = torch.empty((low_rank.shape[0], self.up.shape[1]), device=low_rank.device, dtype=torch.float32)
         ops.channel_gates(out, low_rank, self.up, self.bias, self.inner_tanh, self.kind, self.param)
         return out
 
