@@ -177,8 +177,9 @@ extern "C" int qv_bias_attention_generic(void* out, int ld_out, const void* q, i
 //   portions       a CTA of four warps owns 64 consecutive tokens of one head (16 rows a warp); a block of keys needs
 //                  a strip of 95 consecutive distances of the head's table, which rides in the stage.
 //   single tokens  a CTA of one warp owns the (up to 16) query heads that share a key/value head, and one slice of
-//                  `slice_keys` keys (slices are aligned to absolute positions); with more than one slice a step,
-//                  qv_bias_attention_merge joins the slices in ascending order.
+//                  `slice_keys` keys (slices are aligned to absolute positions; how many there are follows from the longest
+//                  context the step may hold, and those past a token's position leave at once); with more than one slice a
+//                  step, bias_attention_merge_kernel joins a token's slices in ascending order.
 // Key and value sizes: multiples of 8, padded with zeros to NP and DP (64 or 128).
 #define BT_KEYS 32
 
@@ -267,13 +268,7 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
   }
   const int r_lo = warp * 16 + g8, r_hi = r_lo + 8;       // this thread's two rows of the tile
   const bool ok_lo = r_lo < rows_valid, ok_hi = r_hi < rows_valid;
-  if (SINGLE && k_lo >= k_hi) {                           // a slice past the token: nothing to add
-    if (tg == 0) {
-      if (ok_lo) { float* p = a.partial + (((size_t)s * H + h + r_lo) * a.slices + blockIdx.x) * (2 + dv); p[0] = -INFINITY; p[1] = 0.f; }
-      if (ok_hi) { float* p = a.partial + (((size_t)s * H + h + r_hi) * a.slices + blockIdx.x) * (2 + dv); p[0] = -INFINITY; p[1] = 0.f; }
-    }
-    return;
-  }
+  if (SINGLE && k_lo >= k_hi) return;                     // a slice past the token: the merge does not read it
   const size_t width = (size_t)G * (n + dv);
   const size_t k_col = (size_t)kvh * n, v_col = (size_t)G * n + (size_t)kvh * dv;
 
@@ -458,13 +453,15 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
 
 // joins a token's slices (ascending), then gate and factor.  One warp per (token, head).
 __global__ void __launch_bounds__(128) bias_attention_merge_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial,
-                                                                  const int* __restrict__ seg_q_start, int H, int dv, int slices,
+                                                                  const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
+                                                                  int H, int dv, int all_slices, int slice_keys,
                                                                   const float* __restrict__ gate, int ld_g, float factor) {
   pdl_wait();
   pdl_launch_dependents();
   const int s = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= H) return;
-  const float* p = partial + ((size_t)s * H + h) * slices * (2 + dv);
+  const float* p = partial + ((size_t)s * H + h) * all_slices * (2 + dv);
+  const int slices = min(all_slices, seg_pos0[s] / slice_keys + 1);       // the slices that hold keys of this token
   float M = -INFINITY;
   for (int i = 0; i < slices; ++i) M = fmaxf(M, p[(size_t)i * (2 + dv)]);
   float L = 0.f;
@@ -475,7 +472,7 @@ __global__ void __launch_bounds__(128) bias_attention_merge_kernel(bf16* __restr
     float acc = 0.f;
     for (int i = 0; i < slices; ++i) {
       const float* ps = p + (size_t)i * (2 + dv);
-      if (ps[1] > 0.f) acc = fmaf(ps[2 + c], exp2f(ps[0] - M), acc);
+      acc = fmaf(ps[2 + c], exp2f(ps[0] - M), acc);
     }
     float v = acc * inv;
     if (gate) v *= 1.0f / (1.0f + expf(-gate[t * ld_g + (size_t)h * dv + c]));
@@ -525,6 +522,6 @@ extern "C" int qv_bias_attention_mma(void* out, int ld_out, const void* q, int l
   if (rc) return rc;
   if (single && a.slices > 1)
     rc = qv_launch(bias_attention_merge_kernel, dim3(S, (H + 3) / 4), dim3(128), 0, st, (bf16*)out, ld_out, (const float*)partial, seg_q_start,
-                   H, dv, a.slices, gate, ld_g, factor);
+                   seg_pos0, H, dv, a.slices, slice_keys, gate, ld_g, factor);
   return rc;
 }

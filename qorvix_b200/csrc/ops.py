@@ -788,11 +788,13 @@ def bias_attention_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S
 
 
 def bias_attention_slices(tokens: int, G: int, max_ctx: int):
-    """(slices, keys a slice) for single query tokens, so that a step fills the SMs (a warp serves a token, a key/value
-    head and a slice): a function of the step's shape only (a captured step keeps it)."""
-    blocks = max(1, -(-max_ctx // 32))               # the kernel's blocks of keys
-    slices = max(1, min(4 * sm_count() // max(tokens * G, 1), -(-blocks // 2), 32))
-    return slices, -(-blocks // slices) * 32
+    """(slices, keys a slice) for single query tokens (a warp serves a token, a key/value head and a slice): the keys a
+    slice follow from the step's shape, so that few tokens still fill the SMs, and the slices cover the longest context
+    the step may hold (in a captured step: the longest a request may reach; slices past a token's position cost a launch
+    of a warp that leaves at once)."""
+    work = tokens * G
+    keys = 64 if work <= 128 else 128 if work <= 512 else 256
+    return max(1, -(-max_ctx // keys)), keys
 
 
 def bias_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor, table_of_distances=None) -> None:
