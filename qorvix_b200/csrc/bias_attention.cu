@@ -245,7 +245,6 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
   bf16* sV = sK + 2 * BT_KEYS * KS;                       // [2][32][VS]
   float* sB = (float*)(sV + 2 * BT_KEYS * VS);            // [2][96]: the strip of the head's table (portions)
   pdl_wait();
-  pdl_launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g8 = lane >> 2, tg = lane & 3;
   const int H = a.H, G = a.G, n = a.n, dv = a.dv, page = a.page, gs = H / G, far = a.far;
   const int s = blockIdx.z;
@@ -413,6 +412,7 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
     }
     __syncthreads();
   }
+  pdl_launch_dependents();                                // not earlier: the next kernel's waiting CTAs would share the SMs with the tiles
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
 
