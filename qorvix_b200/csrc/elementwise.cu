@@ -615,16 +615,19 @@ extern "C" int qv_embed_pos(float* out, const void* table, const void* pos_table
 }
 
 // ---------------------------------------------------------------- gated feed-forward activations
-// out[t, i] = act(gu[t, i]) * gu[t, f + i]; act 0: SiLU, 1: the tanh form of GELU.  Float32 arithmetic.
+// out[t, i] = act(gate_i) * up_i; act 0: SiLU, 1: the tanh form of GELU.  gu is [gate | up], or with `interleaved` groups of
+// 32 columns: 16 gate values, then the 16 up values of the same features.  Float32 arithmetic.
 template <typename T>
-__global__ void glu_act_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t n, int f, int act) {
+__global__ void glu_act_kernel(T* __restrict__ out, const T* __restrict__ gu, size_t n, int f, int act, int interleaved) {
   pdl_wait();
   pdl_launch_dependents();
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < n; idx += (size_t)gridDim.x * blockDim.x) {
     const size_t t = idx / f;
     const int i = (int)(idx - t * f);
-    const float g = to_f(gu[t * 2 * f + i]);
-    const float u = to_f(gu[t * 2 * f + f + i]);
+    const int gi = interleaved ? ((i >> 4) << 5) + (i & 15) : i;
+    const int ui = interleaved ? gi + 16 : f + i;
+    const float g = to_f(gu[t * 2 * f + gi]);
+    const float u = to_f(gu[t * 2 * f + ui]);
     float a;
     if (act == 1) a = 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     else a = g / (1.0f + expf(-g));
@@ -632,12 +635,12 @@ __global__ void glu_act_kernel(T* __restrict__ out, const T* __restrict__ gu, si
   }
 }
 
-extern "C" int qv_glu_act(void* out, const void* gu, int T, int f, int act, int dt, void* stream) {
+extern "C" int qv_glu_act(void* out, const void* gu, int T, int f, int act, int interleaved, int dt, void* stream) {
   const size_t n = (size_t)T * f;
   if (n == 0) return 0;
-  if (act != 0 && act != 1) return QV_ERR_UNSUPPORTED;
+  if ((act != 0 && act != 1) || (interleaved && (f & 15))) return QV_ERR_UNSUPPORTED;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
-  QV_DISPATCH_DT(dt, TT, return qv_launch(glu_act_kernel<TT>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (TT*)out, (const TT*)gu, n, f, act));
+  QV_DISPATCH_DT(dt, TT, return qv_launch(glu_act_kernel<TT>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (TT*)out, (const TT*)gu, n, f, act, interleaved));
   return QV_ERR_UNSUPPORTED;
 }
 

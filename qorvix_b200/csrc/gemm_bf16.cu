@@ -37,6 +37,7 @@ struct GemmArgs {
   int splits;
   const uint8_t* packed;   // the weight matrix as 16 KB tiles (see qv_pack_weight_tiles), or null
   int bn;                  // persistent kernel: columns of a tile (a multiple of 16, at most its BN)
+  int act = 0;             // the fused activation of a gate/up product: 0 SiLU, 1 the tanh form of GELU
 };
 
 // What the fused rotary epilogue of the QKV product needs: C's columns are H query heads, Hkv key
@@ -71,6 +72,11 @@ struct NormArgs {
 // features); the epilogue writes silu(gate) * up, so C has half as many features as W has rows.
 // bfloat16 output: the fast exponential's error (a few float32 ulp) vanishes in the rounding
 __device__ __forceinline__ float silu_mul(float g, float u) { return __fdividef(g, 1.0f + __expf(-g)) * u; }
+// act 0: silu(g) * u; act 1: gelu_tanh(g) * u = 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u
+__device__ __forceinline__ float glu_mul(float g, float u, int act) {
+  if (act == 0) return silu_mul(g, u);
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * fmaf(0.044715f * g * g, g, g))) * u;
+}
 
 template <int BN, int STAGES, typename TC, bool SWIGLU>
 __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_wide,
@@ -256,7 +262,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
               const float mine = __uint_as_float(r[j]) * (norm.ssq_in ? rs_s[c0 + j] : 1.f);
               const float other = __shfl_xor_sync(0xffffffffu, mine, 16);
               const int t = narrow0 + c0 + j;
-              if (lane < 16 && frow && t < ntok) store_out<TC>(C + (size_t)t * args.ldc + feat, silu_mul(mine, other));
+              if (lane < 16 && frow && t < ntok) store_out<TC>(C + (size_t)t * args.ldc + feat, glu_mul(mine, other, args.act));
             }
           } else if (frow) {
 #pragma unroll
@@ -383,12 +389,12 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
 // One row's 32 accumulator columns from `col` on go to C: as they are (the first `ncols` of them),
 // or, with the fused activation, as the 16 values silu(gate) * up of the features col/2 ...
 template <typename TC, bool SWIGLU>
-__device__ __forceinline__ void store_chunk(TC* C, int ldc, int row, int col, int ncols, const uint32_t* r) {
+__device__ __forceinline__ void store_chunk(TC* C, int ldc, int row, int col, int ncols, const uint32_t* r, int act = 0) {
   if (SWIGLU) {
     TC* dst = C + (size_t)row * ldc + (col >> 1);
     float a[16];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) a[j] = silu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]));
+    for (int j = 0; j < 16; ++j) a[j] = glu_mul(__uint_as_float(r[j]), __uint_as_float(r[16 + j]), act);
     if (sizeof(TC) == 2 && (((uintptr_t)dst) & 15) == 0) {
       uint32_t w[8];
 #pragma unroll
@@ -782,7 +788,7 @@ __global__ void __launch_bounds__(192) gemm_tc_persistent_kernel(const __grid_co
             tmem_ld32(taddr + c0, r);                  // a last chunk of 16 columns reads on into unused ones
             tmem_wait_ld();
             if (row >= M || n0 + c0 >= N) continue;
-            store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, (N - (n0 + c0)) < (bn - c0) ? (N - (n0 + c0)) : (bn - c0), r);
+            store_chunk<TC, SWIGLU>(C, args.ldc, row, n0 + c0, (N - (n0 + c0)) < (bn - c0) ? (N - (n0 + c0)) : (bn - c0), r, args.act);
           }
         }
       }
@@ -924,7 +930,9 @@ static int swap_splits(int tiles, int total_kb, int epilogue, int force_splits, 
 static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* packed, int M, int N, int K, int lda, int ldw, int ldc,
                            int c_dt, int* err, int force_splits, int epilogue, void* stream) {
   // epilogue 0: C[M,N] = A W^T.  epilogue 1: W's rows are 16 gate rows / 16 up rows interleaved and
-  // C[M,N/2] = silu(gate) * up (bfloat16 out, N a multiple of 32).
+  // C[M,N/2] = silu(gate) * up (bfloat16 out, N a multiple of 32).  epilogue 2: as 1 with the tanh form of GELU.
+  const int act = epilogue == 2 ? 1 : 0;
+  if (epilogue == 2) epilogue = 1;
   if (M <= 0 || N <= 0) return 0;
   if (epilogue != 0 && (epilogue != 1 || c_dt != QV_DT_BF16 || (N & 31))) return QV_ERR_UNSUPPORTED;
   if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7)) return QV_ERR_UNSUPPORTED;
@@ -932,7 +940,7 @@ static int gemm_bf16_entry(void* C, const void* A, const void* W, const void* pa
   if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
   cudaStream_t st = (cudaStream_t)stream;
   GemmArgs args;
-  args.C = C; args.err = err; args.packed = nullptr; args.bn = 0;
+  args.C = C; args.err = err; args.packed = nullptr; args.bn = 0; args.act = act;
   args.K = K; args.ldc = ldc;
   const int total_kb = (K + BK - 1) / BK;
   CUtensorMap mw, mn;
@@ -1025,6 +1033,8 @@ extern "C" int qv_gemm_bf16_norm(void* C, const void* A, const void* packed, int
                                  int* err, int epilogue, float* residual, int ld_res, const float* norm_w, float* ssq_out,
                                  const float* ssq_in, int tiles_in, float inv_d, float eps, void* stream) {
   if (M <= 0 || N <= 0) return 0;
+  const int act = epilogue == 2 ? 1 : 0;           // epilogue 2: as 1 with the tanh form of GELU
+  if (epilogue == 2) epilogue = 1;
   if (M > 64 || !packed || (epilogue != 0 && epilogue != 1)) return QV_ERR_UNSUPPORTED;
   if (epilogue == 1 && (c_dt != QV_DT_BF16 || (N & 31))) return QV_ERR_UNSUPPORTED;
   if (c_dt != QV_DT_BF16 && c_dt != QV_DT_F32) return QV_ERR_UNSUPPORTED;
@@ -1038,7 +1048,7 @@ extern "C" int qv_gemm_bf16_norm(void* C, const void* A, const void* packed, int
   const int splits = swap_splits(tiles, total_kb, epilogue, 0, M, residual ? 2 : 1, &per);
   if (residual && splits < 2) return QV_ERR_UNSUPPORTED;
   GemmArgs args;
-  args.C = C; args.err = err; args.packed = (const uint8_t*)packed; args.bn = 0;
+  args.C = C; args.err = err; args.packed = (const uint8_t*)packed; args.bn = 0; args.act = act;
   args.K = K; args.ldc = ldc;
   args.rows_wide = N; args.rows_narrow = M; args.kblocks_per_split = per; args.splits = splits;
   NormArgs na;

@@ -85,7 +85,7 @@ _ARGTYPES = {
     "qv_diff_attention_generic": [_V, _I, _V, _I, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _F, _I, _V],
     "qv_add_tanhnorm": [_V, _V, _V, _V, _V, _F, _V, _I, _I, _I, _I, _I, _V],
     "qv_embed_pos": [_V, _V, _V, _V, _V, _I, _I, _I, _I, _F, _V, _V, _F, _I, _V],
-    "qv_glu_act": [_V, _V, _I, _I, _I, _I, _V],
+    "qv_glu_act": [_V, _V, _I, _I, _I, _I, _I, _V],
     "qv_sigmoid_gate": [_V, _V, _I, _V, _I, _V, _I, _I, _I, _V],
     "qv_depth_mix": [_V, _V, _V, _L, _V, _I, _V],
     "qv_scale": [_V, _L, _F, _V],
@@ -376,12 +376,13 @@ def embed_pos(out, table, pos_table, ids, tok_pos, pos_scale: float = 1.0, weigh
 GLU_SILU, GLU_GELU_TANH = 0, 1
 
 
-def glu_act(out, gu, act: int) -> None:
-    """out[t, i] = act(gu[t, i]) * gu[t, f + i]; act GLU_SILU or GLU_GELU_TANH."""
+def glu_act(out, gu, act: int, interleaved: bool = False) -> None:
+    """out[t, i] = act(gate_i) * up_i; act GLU_SILU or GLU_GELU_TANH; gu is [gate | up], or with `interleaved` groups of
+    32 columns: 16 gate values, then the 16 up values of the same features."""
     _need_cuda(out, gu)
     T, f = out.shape
     assert out.dtype == gu.dtype and out.is_contiguous() and gu.is_contiguous() and tuple(gu.shape) == (T, 2 * f)
-    _check(_lib("elementwise").qv_glu_act(_ptr(out), _ptr(gu), T, f, act, dt_code(out.dtype), _stream()), "glu_act")
+    _check(_lib("elementwise").qv_glu_act(_ptr(out), _ptr(gu), T, f, act, 1 if interleaved else 0, dt_code(out.dtype), _stream()), "glu_act")
 
 
 def sigmoid_gate(out, y, g, bias) -> None:
@@ -1000,7 +1001,7 @@ def gemm_bf16_tc(c, a, w, force_splits: int = 0, swiglu: bool = False) -> bool:
     st = _gemm_buffers(a.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_tc(
         _ptr(c), _ptr(a), _ptr(w), M, N, K, a.stride(0), w.stride(0), c.stride(0), dt_code(c.dtype),
-        _ptr(st["err"]), force_splits, 1 if swiglu else 0, _stream())
+        _ptr(st["err"]), force_splits, int(swiglu), _stream())
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_tc")
@@ -1028,7 +1029,7 @@ def gemm_bf16_packed(c, a, packed, N: int, force_splits: int = 0, swiglu: bool =
     st = _gemm_buffers(a.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_packed(
         _ptr(c), _ptr(a), _ptr(packed), M, N, K, a.stride(0), c.stride(0), dt_code(c.dtype), _ptr(st["err"]),
-        force_splits, 1 if swiglu else 0, _stream())
+        force_splits, int(swiglu), _stream())
     if rc == -2:
         return False
     _check(rc, "gemm_bf16_packed")
@@ -1059,7 +1060,7 @@ def gemm_bf16_norm(c, a, packed, N: int, swiglu: bool = False, residual=None, no
     st = _gemm_buffers(a.device)
     rc = _lib("gemm_bf16").qv_gemm_bf16_norm(
         _ptr(c), _ptr(a), _ptr(packed), M, N, K, a.stride(0), c.stride(0), dt_code(c.dtype), _ptr(st["err"]),
-        1 if swiglu else 0, _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(norm_weight),
+        int(swiglu), _ptr(residual), residual.stride(0) if residual is not None else 0, _ptr(norm_weight),
         _ptr(ssq_out), _ptr(ssq_in), tiles_in, 1.0 / stream_width if stream_width else 0.0, eps, _stream())
     if rc == -2:
         return False
@@ -1179,20 +1180,25 @@ def gemm(out, x, w, packed=None, n: int = 0) -> None:
     gemm_simt(out, x, w)
 
 
-def gemm_swiglu(out, x, w_interleaved, packed=None, n: int = 0) -> None:
-    """out[M,f] = silu(x Wg^T) * (x Wu^T) with gate and up rows interleaved in groups of 16 in
-    w_interleaved [2f, K]: one tensor-core kernel when it takes the shape, else the product followed
+def glu_epilogue(act: int) -> int:
+    """The value of the products' `swiglu` argument that applies `act` (GLU_SILU or GLU_GELU_TANH) in the epilogue."""
+    return 2 if act == GLU_GELU_TANH else 1
+
+
+def gemm_swiglu(out, x, w_interleaved, packed=None, n: int = 0, act: int = 0) -> None:
+    """out[M,f] = act(x Wg^T) * (x Wu^T) (act GLU_SILU or GLU_GELU_TANH) with gate and up rows interleaved in groups
+    of 16 in w_interleaved [2f, K]: one tensor-core kernel when it takes the shape, else the product followed
     by the activation kernel."""
     n = n or w_interleaved.shape[0]
     if x.dtype == torch.bfloat16 and out.dtype == torch.bfloat16:
-        if packed is not None and gemm_bf16_packed(out, x, packed, n, swiglu=True):
+        if packed is not None and gemm_bf16_packed(out, x, packed, n, swiglu=glu_epilogue(act)):
             return
         if (w_interleaved is not None and w_interleaved.dtype == torch.bfloat16
-                and gemm_bf16_tc(out, x, w_interleaved, swiglu=True)):
+                and gemm_bf16_tc(out, x, w_interleaved, swiglu=glu_epilogue(act))):
             return
     gu = torch.empty((x.shape[0], n), device=x.device, dtype=out.dtype)
     gemm(gu, x, w_interleaved, packed, n)
-    swiglu(out, gu, interleaved=True)
+    glu_act(out, gu, act, interleaved=True)
 
 
 def attention_prefill_bf16(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S, max_q_len, H, Hkv, hd, page,

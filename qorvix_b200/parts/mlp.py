@@ -25,7 +25,7 @@ class SwiGLU(FeedForward):
         if name not in acts:
             raise ValueError(f"unknown activation '{name}' (known: {', '.join(acts)})")
         self.act = acts[name]
-        self.interleaved = self.f % 16 == 0 and self.act == ops.GLU_SILU      # the products' epilogue applies SiLU only
+        self.interleaved = self.f % 16 == 0
         if self.interleaved:
             k = g.shape[1]
             fused = torch.stack([g.to(dt).view(self.f // 16, 16, k), u.to(dt).view(self.f // 16, 16, k)], dim=1)
@@ -45,12 +45,12 @@ class SwiGLU(FeedForward):
         act = None
         if isinstance(x, PreNormed):
             act = torch.empty((x.scaled.shape[0], self.f), device=x.scaled.device, dtype=self.rt.dtype)
-            if not (self.interleaved and self.gate_up.forward_prenormed(x, act, swiglu=True)):
+            if not (self.interleaved and self.gate_up.forward_prenormed(x, act, swiglu=ops.glu_epilogue(self.act))):
                 act, x = None, x.materialise()
         if act is None:
             act = torch.empty((x.shape[0], self.f), device=x.device, dtype=self.rt.dtype)
             if self.interleaved:
-                ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed, self.gate_up.out_features)
+                ops.gemm_swiglu(act, x, self.gate_up.weight, self.gate_up.packed, self.gate_up.out_features, act=self.act)
             else:
                 gu = self.gate_up(x, out_dtype=self.rt.dtype)
                 ops.glu_act(act, gu, self.act)
