@@ -26,12 +26,18 @@
 #define GATE_EXP_NEG_SIGMOID 1
 
 // x1 [T, R] (row stride ld_x), W2 transposed [R, N] float32, bias [N] or null -> out [T, N] (row stride ld_out).
-// A CTA takes CG_TOKENS tokens, so that an entry of W2 is read once for all of them; a sum runs over r ascending.
+// A CTA takes CG_TOKENS tokens and CG_CHANNELS channels, so that an entry of W2 is read once for all of its tokens; the sum over r
+// is cut into four quarters (r ascending in each, by four groups of threads) that are added in order, so that a step of
+// few tokens still has many loads in flight and the order of a sum depends on R alone.
 #define CG_TOKENS 8
-__global__ void __launch_bounds__(256) channel_gates_kernel(float* __restrict__ out, int ld_out, const float* __restrict__ x1, int ld_x,
-                                                           const float* __restrict__ w2t, const float* __restrict__ bias, int T, int N,
-                                                           int R, int pre_tanh, int kind, float p) {
-  extern __shared__ float xs[];                    // [CG_TOKENS][R]: the tokens' low-rank rows
+#define CG_CHANNELS 64
+__global__ void __launch_bounds__(4 * CG_CHANNELS) channel_gates_kernel(float* __restrict__ out, int ld_out, const float* __restrict__ x1,
+                                                                       int ld_x, const float* __restrict__ w2t,
+                                                                       const float* __restrict__ bias, int T, int N, int R,
+                                                                       int pre_tanh, int kind, float p) {
+  extern __shared__ float cg_smem[];               // [CG_TOKENS][R] the tokens' low-rank rows, then [4][CG_TOKENS][CG_CHANNELS] partial sums
+  float* xs = cg_smem;
+  float* part = cg_smem + CG_TOKENS * R;
   pdl_wait();
   pdl_launch_dependents();
   const int t0 = blockIdx.x * CG_TOKENS;
@@ -46,45 +52,56 @@ __global__ void __launch_bounds__(256) channel_gates_kernel(float* __restrict__ 
     xs[i] = v;
   }
   __syncthreads();
-  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < N; c += gridDim.y * blockDim.x) {
-    float z[CG_TOKENS];
+  const int cq = threadIdx.x / CG_CHANNELS, cl = threadIdx.x % CG_CHANNELS;
+  const int c = blockIdx.y * CG_CHANNELS + cl;
+  const int rq = (R + 3) / 4;
+  const int r_lo = cq * rq, r_hi = min(R, r_lo + rq);
+  float z[CG_TOKENS];
 #pragma unroll
-    for (int j = 0; j < CG_TOKENS; ++j) z[j] = 0.f;
+  for (int j = 0; j < CG_TOKENS; ++j) z[j] = 0.f;
+  if (c < N) {
 #pragma unroll 8
-    for (int r = 0; r < R; ++r) {
+    for (int r = r_lo; r < r_hi; ++r) {
       const float wv = w2t[(size_t)r * N + c];
 #pragma unroll
       for (int j = 0; j < CG_TOKENS; ++j) z[j] = fmaf(xs[j * R + r], wv, z[j]);
     }
-    const float bc = bias ? bias[c] : 0.f;
+  }
 #pragma unroll
-    for (int j = 0; j < CG_TOKENS; ++j) {
-      if (j >= nt) break;
-      const float zz = z[j] + bc;
-      float g;
-      if (kind == GATE_POW_SIGMOID) {
-        const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));          // log sigmoid(z)
-        g = expf(p * ls);
-      } else {
-        g = expf(-p * (1.0f / (1.0f + expf(-zz))));
-      }
-      out[(size_t)(t0 + j) * ld_out + c] = g;
+  for (int j = 0; j < CG_TOKENS; ++j) part[(cq * CG_TOKENS + j) * CG_CHANNELS + cl] = z[j];
+  __syncthreads();
+  if (c >= N) return;
+  const float bc = bias ? bias[c] : 0.f;
+  for (int j = cq; j < nt; j += 4) {               // the four groups share the tokens' last step
+    float zz = part[j * CG_CHANNELS + cl];
+#pragma unroll
+    for (int q = 1; q < 4; ++q) zz += part[(q * CG_TOKENS + j) * CG_CHANNELS + cl];
+    zz += bc;
+    float g;
+    if (kind == GATE_POW_SIGMOID) {
+      const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));          // log sigmoid(z)
+      g = expf(p * ls);
+    } else {
+      g = expf(-p * (1.0f / (1.0f + expf(-zz))));
     }
+    out[(size_t)(t0 + j) * ld_out + c] = g;
   }
 }
 
 extern "C" int qv_channel_gates(float* out, int ld_out, const float* x1, int ld_x, const float* w2t, const float* bias, int T, int N,
                                 int R, int pre_tanh, int kind, float p, void* stream) {
   if (T <= 0 || N <= 0) return 0;
-  if (R <= 0 || (size_t)CG_TOKENS * R * sizeof(float) > 48 * 1024) return QV_ERR_UNSUPPORTED;
+  const size_t smem = ((size_t)CG_TOKENS * R + 4 * CG_TOKENS * CG_CHANNELS) * sizeof(float);
+  if (R <= 0 || smem > 48 * 1024) return QV_ERR_UNSUPPORTED;
   if (kind != GATE_POW_SIGMOID && kind != GATE_EXP_NEG_SIGMOID) return QV_ERR_UNSUPPORTED;
-  const int by = (N + 255) / 256 < 64 ? (N + 255) / 256 : 64;
+  const int by = (N + CG_CHANNELS - 1) / CG_CHANNELS;
+  if (by > 65535) return QV_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
   const int per = 65535 * CG_TOKENS;
   for (int done = 0; done < T; done += per) {
     const int rows = T - done < per ? T - done : per;
-    const int rc = qv_launch(channel_gates_kernel, dim3((rows + CG_TOKENS - 1) / CG_TOKENS, by), dim3(256), (size_t)CG_TOKENS * R * sizeof(float),
-                             st, out + (size_t)done * ld_out, ld_out, x1 + (size_t)done * ld_x, ld_x, w2t, bias, rows, N, R, pre_tanh, kind, p);
+    const int rc = qv_launch(channel_gates_kernel, dim3((rows + CG_TOKENS - 1) / CG_TOKENS, by), dim3(4 * CG_CHANNELS), smem, st,
+                             out + (size_t)done * ld_out, ld_out, x1 + (size_t)done * ld_x, ld_x, w2t, bias, rows, N, R, pre_tanh, kind, p);
     if (rc) return rc;
   }
   return 0;
