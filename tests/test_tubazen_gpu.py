@@ -13,6 +13,7 @@ from qorvix_b200 import LLM, ModelRunner, SamplingParams, StepEntry
 from qorvix_b200.cache import CacheManager
 from qorvix_b200.cache.manager import CompositeCacheView
 from qorvix_b200.config import lookup_architecture
+from qorvix_b200.csrc import ops
 from qorvix_b200.engine.batch import BatchBuilder
 from qorvix_b200.parts import Runtime, build_part
 from qorvix_b200.weights import TensorSource
@@ -531,3 +532,120 @@ def test_greedy_generation_through_the_scheduler(models, name, dtype):
             full = plain_logits(m, seq)[-1]
             assert float(full[tok]) >= float(full.max()) - slack * float(full.abs().max()), f"token {i} of a prompt of {len(p)}: {tok}, plain {int(full.argmax())}"
             seq.append(tok)
+
+
+# ---------------------------------------------------------------------------------------------- kernels alone, larger shapes
+
+def step_ctx(seg_lens, pos0):
+    """A step's context for kernels run alone: segments in the given order, every one with its own state slot."""
+    from types import SimpleNamespace
+    i32 = dict(dtype=torch.int32, device=DEV)
+    qs = [0]
+    for n in seg_lens:
+        qs.append(qs[-1] + n)
+    return SimpleNamespace(
+        num_segments=len(seg_lens), num_tokens=qs[-1], max_q_len=max(seg_lens), seg_len=list(seg_lens), seg_start_pos=list(pos0),
+        max_ctx_len=max(p + n for p, n in zip(pos0, seg_lens)), captured=False, seg_q_start=torch.tensor(qs, **i32),
+        seg_pos0=torch.tensor(pos0, **i32), seg_slot=torch.arange(len(seg_lens), **i32),
+        tok_seg=torch.cat([torch.full((n,), s, **i32) for s, n in enumerate(seg_lens)]),
+        tok_pos=torch.cat([torch.arange(p, p + n, **i32) for p, n in zip(pos0, seg_lens)]))
+
+
+@pytest.mark.parametrize("H,G,n,dv", [(16, 1, 128, 128), (8, 2, 64, 128), (4, 4, 104, 24), (6, 3, 16, 64)])
+def test_tensor_core_attention_on_long_contexts_and_unequal_segments(H, G, n, dv, monkeypatch):
+    """Single tokens at contexts from 1 to several hundred (many slices, some empty) ahead of portions that start in the
+    middle of a context, pages scattered over the pool; every (token, head) against float64 sums over its own keys."""
+    from qorvix_b200.parts.bias_attention import distance_buckets
+    page, rows, far, scale = 16, 10, 150.0, 0.3
+    seg_lens, pos0 = [1, 1, 1, 1, 70, 3, 129], [0, 31, 64, 700, 390, 255, 0]
+    ctx = step_ctx(seg_lens, pos0)
+    S, T = len(seg_lens), sum(seg_lens)
+    blocks = -(-ctx.max_ctx_len // page)
+    g = torch.Generator().manual_seed(5)
+    order = torch.randperm(S * blocks, generator=g).to(torch.int32).view(S, blocks)          # no request's pages lie in a row
+    cache = (torch.randn(S * blocks + 1, page, G * (n + dv), generator=g) * 0.7).to(torch.bfloat16)
+    q = torch.randn(T, H * n, generator=g).to(torch.bfloat16)
+    gate = torch.randn(T, H * dv, generator=g)
+    rel = torch.randn(rows, H, generator=g) * 2
+    bucket = torch.from_numpy(distance_buckets(rows, far, 1024))
+    out = torch.empty(T, H * dv, dtype=torch.bfloat16, device=DEV)
+    table = ops.bias_attention_table(bucket.to(DEV), rel.to(DEV))
+
+    def no_other_kernel(*a, **k):
+        raise AssertionError("these sizes belong to the tensor-core kernel")
+    monkeypatch.setattr(ops, "bias_attention_generic", no_other_kernel)
+    ops.bias_attention(out, q.to(DEV), cache.to(DEV), ctx, order.to(DEV), H, G, n, dv, page, scale, bucket.to(DEV), rel.to(DEV),
+                       gate.to(DEV), 0.9, table_of_distances=table)
+    ops.check_kernel_errors()
+    want = torch.zeros(T, H * dv, dtype=torch.float64)
+    t = 0
+    for s, (m, p0) in enumerate(zip(seg_lens, pos0)):
+        L = p0 + m
+        rows_of = torch.stack([cache[int(order[s, j // page]), j % page] for j in range(L)]).double()     # [L, G * (n + dv)]
+        for i in range(m):
+            pos = p0 + i
+            for h in range(H):
+                kv = h // (H // G)
+                k, v = rows_of[: pos + 1, kv * n: (kv + 1) * n], rows_of[: pos + 1, G * n + kv * dv: G * n + (kv + 1) * dv]
+                dist = torch.arange(pos, -1, -1).clamp(max=len(bucket) - 1)
+                sc = (k @ q[t, h * n: (h + 1) * n].double()) * scale + rel[bucket[dist].long(), h].double()
+                o = torch.softmax(sc, 0) @ v
+                want[t, h * dv: (h + 1) * dv] = o * torch.sigmoid(gate[t, h * dv: (h + 1) * dv].double()) * 0.9
+            t += 1
+    close(out.float(), want, torch.bfloat16, "attention", loose=0.5)
+
+
+@pytest.mark.parametrize("removal", [False, True])
+@pytest.mark.parametrize("H,dk,dv", [(2, 256, 20), (3, 64, 72), (1, 12, 130), (5, 100, 8)])
+def test_channel_scan_with_unequal_segments_and_carried_states(H, dk, dv, removal):
+    """Single tokens beside portions longer than a stage of the ring, every segment from a state of its own that is not
+    zero; outputs and the states left behind against the recurrence written out in float64."""
+    seg_lens = [1, 1, 45, 2, 16, 33]
+    ctx = step_ctx(seg_lens, [0] * len(seg_lens))
+    S, T = len(seg_lens), sum(seg_lens)
+    g = torch.Generator().manual_seed(dk + dv)
+    f = lambda *shape: torch.randn(*shape, generator=g)
+    q, k, v = f(T, H * dk) * 0.3, f(T, H * dk) * 0.3, f(T, H * dv)
+    w = torch.sigmoid(f(T, H * dk) + 2)
+    u = torch.nn.functional.normalize(f(T, H, dk), dim=-1).reshape(T, H * dk)
+    au = u * torch.sigmoid(f(T, H * dk))
+    n_state = ops.channel_scan_state_floats(H, dk, dv)
+    state = torch.zeros(S, n_state, device=DEV)
+    y = torch.empty(T, H * dv, device=DEV)
+    dev = lambda x: x.to(DEV).contiguous()
+    args = (dev(q), dev(k), dev(v), dev(w), dev(au) if removal else None, dev(u) if removal else None, 0.5)
+    ops.channel_scan(y, *args, state, ctx, H, dk, dv)              # a first step leaves states that are not zero
+    y2 = torch.empty_like(y)
+    ops.channel_scan(y2, *args, state, ctx, H, dk, dv)             # the same tokens again, from those states
+    ops.check_kernel_errors()
+    want = torch.zeros(2, T, H * dv, dtype=torch.float64)
+    t0 = 0
+    for m in seg_lens:
+        for h in range(H):
+            Sm = torch.zeros(dk, dv, dtype=torch.float64)
+            for rep in range(2):
+                for t in range(t0, t0 + m):
+                    sl = slice(h * dk, (h + 1) * dk)
+                    new = w[t, sl].double()[:, None] * Sm + k[t, sl].double()[:, None] * v[t, h * dv: (h + 1) * dv].double()[None, :]
+                    if removal:
+                        new = new - au[t, sl].double()[:, None] * (u[t, sl].double() @ Sm)[None, :]
+                    Sm = new
+                    want[rep, t, h * dv: (h + 1) * dv] = (Sm.T @ q[t, sl].double()) * 0.5
+        t0 += m
+    close(y, want[0], torch.float32, "first step")
+    close(y2, want[1], torch.float32, "second step")
+
+
+@pytest.mark.parametrize("T,N,R", [(1, 70, 5), (8, 64, 64), (19, 300, 7), (9, 2048, 33)])
+@pytest.mark.parametrize("form", ["pow_sigmoid", "exp_neg_sigmoid"])
+def test_channel_gates_alone(T, N, R, form):
+    g = torch.Generator().manual_seed(T + N)
+    x1, w2, b = torch.randn(T, R + 3, generator=g), torch.randn(N, R, generator=g) * 0.5, torch.randn(N, generator=g)
+    out = torch.empty(T, N, device=DEV)
+    inner = form == "exp_neg_sigmoid"
+    kind, p = (ops.GATE_POW_SIGMOID, 1 / 7.0) if form == "pow_sigmoid" else (ops.GATE_EXP_NEG_SIGMOID, 0.6)
+    ops.channel_gates(out, x1.to(DEV)[:, 1: 1 + R], w2.t().contiguous().to(DEV), b.to(DEV), inner, kind, p)
+    xin = x1[:, 1: 1 + R].double()
+    z = (torch.tanh(xin) if inner else xin) @ w2.double().t() + b.double()
+    want = torch.sigmoid(z) ** (1 / 7.0) if form == "pow_sigmoid" else torch.exp(-0.6 * torch.sigmoid(z))
+    close(out, want, torch.float32, "gates")
