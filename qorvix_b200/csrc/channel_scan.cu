@@ -244,6 +244,7 @@ __global__ void __launch_bounds__(32 * CS_WARPS) channel_scan_kernel(ChannelScan
     __syncthreads();
     const int j0 = c * chunk, nt = min(chunk, len - j0);
     if (active) {
+#pragma unroll(REMOVAL ? 2 : 4)
       for (int j = 0; j < nt; ++j) {
         const float* d = cs_ring + ((size_t)(c & 1) * chunk + j) * ROW;
         const float4* pw = (const float4*)(d + lic * CS_PAD);
