@@ -385,9 +385,9 @@ def bias_prepare_case(T, peaks, page=16) -> dict:
     return kb._figures(us, T * (cols * 4 + width * 2 + H * n * 2), 0.0, peaks)
 
 
-def channel_scan_case(kind, seg_lens, peaks) -> dict:
+def channel_scan_case(kind, seg_lens, peaks, scan_only=False) -> dict:
     """The recurrence with a decay per key channel: gated linear attention ('gla') or the delta rule ('delta'), with the kernels that
-    form its decays (and unit keys) and the norm behind it."""
+    form its decays (and unit keys) and the norm behind it, or (scan_only) the recurrence's kernel alone."""
     S, T = len(seg_lens), sum(seg_lens)
     ctx = _ctx(seg_lens, [0] * S)
     if kind == "gla":
@@ -406,8 +406,14 @@ def channel_scan_case(kind, seg_lens, peaks) -> dict:
     y = torch.empty(T, H * dv, **f32)
     out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
 
+    ops.channel_gates(w, low, w2, wb, kind != "gla", ops.GATE_POW_SIGMOID if kind == "gla" else ops.GATE_EXP_NEG_SIGMOID, 0.0625 if kind == "gla" else 0.6065)
+    ops.unit_keys(u, au, k, a, wb, H, dk, 1e-6)
+
     def run(i):
-        if kind == "gla":
+        if scan_only:
+            rem = kind != "gla"
+            ops.channel_scan(y, q, k, v, w, au if rem else None, u if rem else None, 1.0, states[i % copies], ctx, H, dk, dv)
+        elif kind == "gla":
             ops.channel_gates(w, low, w2, wb, False, ops.GATE_POW_SIGMOID, 1.0 / 16.0)
             ops.channel_scan(y, q, k, v, w, None, None, dk ** -0.5, states[i % copies], ctx, H, dk, dv)
             ops.head_norm_gate(out, y, g, nw, H, 1e-5, ops.HEAD_GATE_SILU)
@@ -418,6 +424,9 @@ def channel_scan_case(kind, seg_lens, peaks) -> dict:
             ops.head_norm_gate(out, y, g, nw, H, 1e-5, ops.HEAD_GATE_SIGMOID)
 
     us = kb.timed_chain(run, launches=6)
+    if scan_only:
+        vecs = (3 if kind == "gla" else 5) * H * dk + 2 * H * dv
+        return kb._figures(us, 2 * S * n_state * 4 + T * vecs * 4, (4.0 if kind == "gla" else 8.0) * T * H * dk * dv, peaks)
     vecs = (3 if kind == "gla" else 4) * H * dk + 2 * H * dv
     nbytes = 2 * S * n_state * 4 + T * vecs * 4 + T * H * dv * 2
     return kb._figures(us, nbytes, (4.0 if kind == "gla" else 8.0) * T * H * dk * dv, peaks)
@@ -434,6 +443,10 @@ def run_tubazen(args, peaks) -> dict:
         f"bias_prepare_t{T}": bias_prepare_case(T, peaks), f"bias_prepare_t{B}": bias_prepare_case(B, peaks),
         f"gla_scan_prefill_t{T}": channel_scan_case("gla", [T], peaks), f"gla_scan_decode_b{B}": channel_scan_case("gla", [1] * B, peaks),
         f"delta_scan_prefill_t{T}": channel_scan_case("delta", [T], peaks), f"delta_scan_decode_b{B}": channel_scan_case("delta", [1] * B, peaks),
+        # the recurrence's kernel alone, as the other designs' recurrences are timed
+        f"gla_scan_alone_prefill_t{T}": channel_scan_case("gla", [T], peaks, True), f"gla_scan_alone_decode_b{B}": channel_scan_case("gla", [1] * B, peaks, True),
+        f"delta_scan_alone_prefill_t{T}": channel_scan_case("delta", [T], peaks, True),
+        f"delta_scan_alone_decode_b{B}": channel_scan_case("delta", [1] * B, peaks, True),
     }
     # the like kernels of the other designs: the differential attention and the recurrences with one decay a head
     res["like_kernels"] = {
