@@ -283,14 +283,17 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
   auto load = [&](int stage, int j0) {
     bf16* dK = sK + stage * BT_KEYS * KS;
     bf16* dV = sV + stage * BT_KEYS * VS;
-    for (int idx = tid; idx < BT_KEYS * (KC + VC); idx += NT) {
+    // lane r of every warp works out where key j0 + r lies (one division a block and lane); the pieces of 16 bytes ask for it
+    const int jr = j0 + lane;
+    unsigned long long row_at = 0;
+    if (jr < k_hi) row_at = ((unsigned long long)bt[jr / page] * page + (unsigned long long)(jr % page)) * width;
+    for (int idx = tid; idx < BT_KEYS * (KC + VC); idx += NT) {       // the same number of rounds for every lane: (KC + VC) % 4 == 0
       const int r = idx / (KC + VC), c = idx % (KC + VC);
-      const int j = j0 + r;
+      const unsigned long long at = __shfl_sync(0xffffffffu, row_at, r);
       const bool isk = c < KC;
       const int cc = isk ? c : c - KC;
-      const bool valid = j < k_hi && cc * 8 < (isk ? n : dv);
-      const bf16* src = a.cache;
-      if (valid) src = a.cache + ((size_t)bt[j / page] * page + (size_t)(j % page)) * width + (isk ? k_col : v_col) + cc * 8;
+      const bool valid = j0 + r < k_hi && cc * 8 < (isk ? n : dv);
+      const bf16* src = valid ? a.cache + at + (isk ? k_col : v_col) + cc * 8 : a.cache;
       bt_cp16(isk ? dK + r * KS + cc * 8 : dV + r * VS + cc * 8, src, valid);
     }
     if (!SINGLE) {
