@@ -220,14 +220,12 @@ __device__ __forceinline__ uint32_t bt_pack(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
   return *(uint32_t*)&h;
 }
-// the three bfloat16 terms of two float32 weights
+// the three bfloat16 terms of two float32 weights (a pair is rounded by one instruction; its halves are floats again by a shift and a mask)
 __device__ __forceinline__ void bt_split3(float x, float y, uint32_t& t0, uint32_t& t1, uint32_t& t2) {
-  const float x0 = __bfloat162float(__float2bfloat16_rn(x)), y0 = __bfloat162float(__float2bfloat16_rn(y));
-  const float xr = x - x0, yr = y - y0;
-  const float x1 = __bfloat162float(__float2bfloat16_rn(xr)), y1 = __bfloat162float(__float2bfloat16_rn(yr));
-  t0 = bt_pack(x0, y0);
-  t1 = bt_pack(x1, y1);
-  t2 = bt_pack(xr - x1, yr - y1);
+  t0 = bt_pack(x, y);
+  const float xr = x - __uint_as_float(t0 << 16), yr = y - __uint_as_float(t0 & 0xffff0000u);
+  t1 = bt_pack(xr, yr);
+  t2 = bt_pack(xr - __uint_as_float(t1 << 16), yr - __uint_as_float(t1 & 0xffff0000u));
 }
 
 static inline size_t bt_smem_bytes(int NP, int DP, int warps) {
