@@ -321,7 +321,7 @@ def run_lotirax(args, peaks) -> dict:
 # ------------------------------------------------------------------ Tubazen
 # Gated linear attention with eight heads of 128 key channels over 256 values; attention with a distance bias, 16 heads of
 # 128 on 4 key/value heads, beside a delta rule of 32 heads of 64; gated feed-forwards of 5,632.
-TUB_GLA = {"heads": 8, "dim": 128, "vdim": 256, "tau": 16.0, "rank": 64}
+TUB_GLA = {"heads": 8, "dim": 128, "vdim": 256, "tau": 8.0, "rank": 64}
 TUB_LEFT = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "bias_max": 4096, "bias_rows": 64,
             "q_temp": {"coef": 0.2, "every": 512}}
 TUB_RIGHT = {"heads": 32, "dim": 64, "rank": 64}
@@ -406,7 +406,7 @@ def channel_scan_case(kind, seg_lens, peaks, scan_only=False) -> dict:
     y = torch.empty(T, H * dv, **f32)
     out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
 
-    ops.channel_gates(w, low, w2, wb, kind != "gla", ops.GATE_POW_SIGMOID if kind == "gla" else ops.GATE_EXP_NEG_SIGMOID, 0.0625 if kind == "gla" else 0.6065)
+    ops.channel_gates(w, low, w2, wb, kind != "gla", ops.GATE_POW_SIGMOID if kind == "gla" else ops.GATE_EXP_NEG_SIGMOID, 0.125 if kind == "gla" else 0.6065)
     ops.unit_keys(u, au, k, a, wb, H, dk, 1e-6)
 
     def run(i):
@@ -414,7 +414,7 @@ def channel_scan_case(kind, seg_lens, peaks, scan_only=False) -> dict:
             rem = kind != "gla"
             ops.channel_scan(y, q, k, v, w, au if rem else None, u if rem else None, 1.0, states[i % copies], ctx, H, dk, dv)
         elif kind == "gla":
-            ops.channel_gates(w, low, w2, wb, False, ops.GATE_POW_SIGMOID, 1.0 / 16.0)
+            ops.channel_gates(w, low, w2, wb, False, ops.GATE_POW_SIGMOID, 1.0 / 8.0)
             ops.channel_scan(y, q, k, v, w, None, None, dk ** -0.5, states[i % copies], ctx, H, dk, dv)
             ops.head_norm_gate(out, y, g, nw, H, 1e-5, ops.HEAD_GATE_SILU)
         else:

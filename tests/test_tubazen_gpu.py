@@ -300,13 +300,13 @@ def test_one_far_token_in_the_state(kind, dtype):
 
 
 LEFT_CASES = [th.left(), th.left(heads=6, kv_heads=1, dim=8, vdim=8, bias_max=23, rows=9, coef=1.1, every=3),
-              th.left(heads=1, kv_heads=1, dim=36, vdim=20, bias_max=200, rows=32, coef=0.3, every=1000),
+              th.left(heads=1, kv_heads=1, dim=36, vdim=20, bias_max=200, rows=32, coef=0.35, every=1000),
               th.left(heads=4, kv_heads=4, dim=32, vdim=64, bias_max=40, rows=16, every=16),
               th.left(heads=8, kv_heads=2, dim=16, vdim=32, bias_max=90, rows=20, every=5),
               th.left(heads=4, kv_heads=2, dim=64, vdim=128, bias_max=60.5, rows=11, coef=0.0, every=1),
               th.left(heads=3, kv_heads=3, dim=128, vdim=16, bias_max=3, rows=2, coef=2.0, every=2),
               th.left(heads=2, kv_heads=1, dim=21, vdim=13, bias_max=77, rows=15, every=40),
-              th.left(heads=16, kv_heads=1, dim=48, vdim=56, bias_max=30, rows=12, every=9),          # sixteen heads share the keys
+              th.left(heads=16, kv_heads=1, dim=40, vdim=56, bias_max=30, rows=12, every=9),          # sixteen heads share the keys
               th.left(heads=34, kv_heads=2, dim=8, vdim=72, bias_max=100, rows=6, coef=0.7, every=11),  # seventeen do
               th.left(heads=2, kv_heads=2, dim=72, vdim=8, bias_max=64, rows=64, every=32)]
 

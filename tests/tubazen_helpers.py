@@ -61,9 +61,9 @@ CONFIG_A = config([layer(gla(), dense()), layer(pair(), dense(ff=40)), layer(gla
                    layer(pair(left(heads=6, kv_heads=1, dim=8, vdim=8, bias_max=23, rows=9, coef=1.1, every=3), right(heads=3, dim=40, rank=2),
                               left_scale=0.6, right_scale=1.7), dense(ff=50))])
 # B: side-by-side layers first, one head everywhere, factor one on the logits, temperature steps longer than the prompts
-CONFIG_B = config([layer(pair(left(heads=1, kv_heads=1, dim=36, vdim=20, bias_max=200, rows=32, coef=0.3, every=1000), right(heads=1, dim=64, rank=16),
+CONFIG_B = config([layer(pair(left(heads=1, kv_heads=1, dim=36, vdim=20, bias_max=200, rows=32, coef=0.35, every=1000), right(heads=1, dim=64, rank=16),
                               left_scale=1.0, right_scale=1.0), dense(ff=24)),
-                   layer(gla(heads=1, dim=64, vdim=64, tau=16.0, rank=16), dense(ff=96))],
+                   layer(gla(heads=1, dim=64, vdim=64, tau=12.0, rank=16), dense(ff=96))],
                   vocab=150, width=48, eps=1e-6, logit_scale=1.0)
 # C: sizes in multiples of 16 and 32; only side-by-side layers; the bias table ends before the longest distance
 CONFIG_C = config([layer(pair(left(heads=4, kv_heads=4, dim=32, vdim=64, bias_max=40, rows=16, every=16), right(heads=2, dim=32, rank=8)), dense(ff=96)),
