@@ -763,6 +763,8 @@ def bias_attention_tc(out, q, cache_layer, seg_q_start, seg_pos0, block_table, S
     table: bias_attention_table(...).  False, nothing written, for sizes it does not take."""
     if q.dtype != torch.bfloat16 or n % 8 or dv % 8 or n > 128 or dv > 128 or q.stride(0) % 8 or out.stride(0) % 2:
         return False
+    if q.data_ptr() % 16 or out.data_ptr() % 4:        # 16-byte copies of q, paired stores of the outputs
+        return False
     if max_q_len == 1 and H // G > 16:
         return False
     _need_cuda(out, q, cache_layer, seg_q_start, seg_pos0, block_table, table, gate)
