@@ -9,6 +9,8 @@
 //
 // qv_bias_attn_prepare      adds the projections' biases, scales q by the temperature of its position (float32, then rounded to
 //                           the compute type) and writes k and v into the token's cache row.
+// qv_rot_norm_prepare       for attention without a bias table over the same cache rows: rotation of part of every head, unit
+//                           norm of q and k, a temperature per head on q, values blended with another layer's.
 // qv_bias_attention_generic one warp per (token, head), keys in blocks of 32 aligned to absolute positions, float32 throughout:
 //                           the order of every sum depends on the token's position alone.
 #include "common.cuh"
@@ -62,6 +64,95 @@ extern "C" int qv_bias_attn_prepare(void* q_out, int ld_qo, const float* proj, i
                                   (TT*)((char*)q_out + (size_t)done * ld_qo * esz), ld_qo, proj + (size_t)done * ld_p, ld_p, q_off, k_off,
                                   v_off, bq, bk, bv, (TT*)cache, tok_pos + done, tok_seg + done, block_table, max_blocks, H, G, n, dv,
                                   page, coef, every));
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// Queries and keys that are rotated and then unit-normed, values that may be blended with another layer's:
+//   q, k heads: the first `rot` entries rotated in split halves (entry i with entry i + rot/2, angles of row tok_pos of cos_sin),
+//   then, if `unit`, divided by the root mean square over the head (eps under the root); q also times head_temp[h] (or 1);
+//   v = (1 - lam) v + lam v_first[t] where v_first is given (float32 [T, G * dv], row stride ld_vf).
+// proj [T, ...] float32 with [q | k | v] at q_off, k_off, v_off; q -> q_out (compute type), k and v -> the token's cache row
+// [G * n | G * dv].  All arithmetic float32.  One block per token, a warp per head in turn (staged in shared memory).
+template <typename T>
+__global__ void __launch_bounds__(256) rot_norm_prepare_kernel(T* __restrict__ q_out, int ld_qo, const float* __restrict__ proj, int ld_p,
+                                                              int q_off, int k_off, int v_off, T* __restrict__ cache,
+                                                              const float2* __restrict__ cos_sin, int table_rows, int rot, int unit,
+                                                              float eps, const float* __restrict__ head_temp,
+                                                              const float* __restrict__ v_first, int ld_vf, float lam,
+                                                              const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
+                                                              const int* __restrict__ block_table, int max_blocks, int H, int G, int n,
+                                                              int dv, int page) {
+  extern __shared__ float rn_smem[];               // 8 warps x n floats
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int pos = tok_pos[t];
+  const float* row = proj + (size_t)t * ld_p;
+  const int half = rot >> 1;
+  const float2* cs = rot ? cos_sin + (size_t)(pos < table_rows ? pos : table_rows - 1) * half : nullptr;
+  const int nk = G * n, nv = G * dv;
+  const int pg = block_table[(size_t)tok_seg[t] * max_blocks + pos / page];
+  T* crow = cache + ((size_t)pg * page + (size_t)(pos % page)) * ((size_t)nk + nv);
+  float* x = rn_smem + (size_t)warp * n;
+  for (int hs = warp; hs < H + G; hs += 8) {
+    const bool isq = hs < H;
+    const float* src = isq ? row + q_off + (size_t)hs * n : row + k_off + (size_t)(hs - H) * n;
+    for (int i = lane; i < n; i += 32) x[i] = src[i];
+    __syncwarp();
+    for (int i = lane; i < half; i += 32) {
+      const float a = x[i], b = x[i + half];
+      const float2 c = cs[i];
+      x[i] = a * c.x - b * c.y;
+      x[i + half] = b * c.x + a * c.y;
+    }
+    __syncwarp();
+    float sc = 1.0f;
+    if (unit) {
+      float ss = 0.f;
+      for (int i = lane; i < n; i += 32) ss = fmaf(x[i], x[i], ss);
+      ss = warp_sum(ss);
+      sc = 1.0f / sqrtf(ss / (float)n + eps);
+    }
+    if (isq) {
+      const float temp = head_temp ? head_temp[hs] : 1.0f;
+      T* dst = q_out + (size_t)t * ld_qo + (size_t)hs * n;
+      for (int i = lane; i < n; i += 32) dst[i] = from_f<T>(x[i] * sc * temp);
+    } else {
+      T* dst = crow + (size_t)(hs - H) * n;
+      for (int i = lane; i < n; i += 32) dst[i] = from_f<T>(x[i] * sc);
+    }
+    __syncwarp();
+  }
+  const float* vf = v_first ? v_first + (size_t)t * ld_vf : nullptr;
+  for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+    float v = row[v_off + i];
+    if (vf) v = (1.0f - lam) * v + lam * vf[i];
+    crow[nk + i] = from_f<T>(v);
+  }
+}
+
+extern "C" int qv_rot_norm_prepare(void* q_out, int ld_qo, const float* proj, int ld_p, int q_off, int k_off, int v_off, void* cache,
+                                   const float* cos_sin, int table_rows, int rot, int unit, float eps, const float* head_temp,
+                                   const float* v_first, int ld_vf, float lam, const int* tok_pos, const int* tok_seg,
+                                   const int* block_table, int max_blocks, int T, int H, int G, int n, int dv, int page, int dt,
+                                   void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || n <= 0 || dv <= 0 || rot < 0 || rot > n || (rot & 1) || (rot && cos_sin == nullptr)) return QV_ERR_UNSUPPORTED;
+  const size_t smem = (size_t)8 * n * sizeof(float);
+  if (smem > 48 * 1024) return QV_ERR_TOO_LARGE;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t esz = dt == QV_DT_F32 ? 4 : 2;
+  for (int done = 0; done < T; done += 65535) {
+    const int rows = T - done < 65535 ? T - done : 65535;
+    int rc = QV_ERR_UNSUPPORTED;
+    QV_DISPATCH_DT(dt, TT,
+                   rc = qv_launch(rot_norm_prepare_kernel<TT>, dim3(rows), dim3(256), smem, st,
+                                  (TT*)((char*)q_out + (size_t)done * ld_qo * esz), ld_qo, proj + (size_t)done * ld_p, ld_p, q_off, k_off,
+                                  v_off, (TT*)cache, (const float2*)cos_sin, table_rows, rot, unit, eps, head_temp,
+                                  v_first ? v_first + (size_t)done * ld_vf : nullptr, ld_vf, lam, tok_pos + done, tok_seg + done,
+                                  block_table, max_blocks, H, G, n, dv, page));
     if (rc) return rc;
   }
   return 0;

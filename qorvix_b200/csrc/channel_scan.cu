@@ -8,6 +8,8 @@
 // qv_channel_gates    per-channel factors from a low-rank pre-activation: z = W2 f(x1) + b, then
 //                       POW_SIGMOID      sigmoid(z)^p                  (a decay with temperature 1/p)
 //                       EXP_NEG_SIGMOID  exp(-p * sigmoid(z))          (a decay bounded below by exp(-p))
+//                       EXP_NEG_SOFTPLUS exp(-rate_c * softplus(z))    (a step size times a rate per channel)
+//                       LINEAR           z                             (a pre-activation for a later kernel)
 //                     f the identity or tanh.
 // qv_unit_keys        u = k / sqrt(sum(k^2) + eps) per head and au = sigmoid(a + bias) * u.
 // qv_channel_scan     the recurrence.  The columns of S are independent of one another: a few lanes own a column, each a run of
@@ -24,6 +26,8 @@
 
 #define GATE_POW_SIGMOID 0
 #define GATE_EXP_NEG_SIGMOID 1
+#define GATE_EXP_NEG_SOFTPLUS 2
+#define GATE_LINEAR 3
 
 // x1 [T, R] (row stride ld_x), W2 transposed [R, N] float32, bias [N] or null -> out [T, N] (row stride ld_out).
 // A CTA takes CG_TOKENS tokens and CG_CHANNELS channels, so that an entry of W2 is read once for all of its tokens; the sum over r
@@ -34,7 +38,7 @@
 __global__ void __launch_bounds__(4 * CG_CHANNELS) channel_gates_kernel(float* __restrict__ out, int ld_out, const float* __restrict__ x1,
                                                                        int ld_x, const float* __restrict__ w2t,
                                                                        const float* __restrict__ bias, int T, int N, int R,
-                                                                       int pre_tanh, int kind, float p) {
+                                                                       int pre_tanh, int kind, float p, const float* __restrict__ rate) {
   extern __shared__ float cg_smem[];               // [CG_TOKENS][R] the tokens' low-rank rows, then [4][CG_TOKENS][CG_CHANNELS] partial sums
   float* xs = cg_smem;
   float* part = cg_smem + CG_TOKENS * R;
@@ -81,19 +85,25 @@ __global__ void __launch_bounds__(4 * CG_CHANNELS) channel_gates_kernel(float* _
     if (kind == GATE_POW_SIGMOID) {
       const float ls = fminf(zz, 0.f) - log1pf(expf(-fabsf(zz)));          // log sigmoid(z)
       g = expf(p * ls);
-    } else {
+    } else if (kind == GATE_EXP_NEG_SIGMOID) {
       g = expf(-p * (1.0f / (1.0f + expf(-zz))));
+    } else if (kind == GATE_EXP_NEG_SOFTPLUS) {
+      const float sp = fmaxf(zz, 0.f) + log1pf(expf(-fabsf(zz)));          // softplus(z)
+      g = expf(-rate[c] * sp);
+    } else {
+      g = zz;
     }
     out[(size_t)(t0 + j) * ld_out + c] = g;
   }
 }
 
+// rate [N] float32: the factor per channel of GATE_EXP_NEG_SOFTPLUS (null for the other kinds).
 extern "C" int qv_channel_gates(float* out, int ld_out, const float* x1, int ld_x, const float* w2t, const float* bias, int T, int N,
-                                int R, int pre_tanh, int kind, float p, void* stream) {
+                                int R, int pre_tanh, int kind, float p, const float* rate, void* stream) {
   if (T <= 0 || N <= 0) return 0;
   const size_t smem = ((size_t)CG_TOKENS * R + 4 * CG_TOKENS * CG_CHANNELS) * sizeof(float);
   if (R <= 0 || smem > 48 * 1024) return QV_ERR_UNSUPPORTED;
-  if (kind != GATE_POW_SIGMOID && kind != GATE_EXP_NEG_SIGMOID) return QV_ERR_UNSUPPORTED;
+  if (kind < GATE_POW_SIGMOID || kind > GATE_LINEAR || (kind == GATE_EXP_NEG_SOFTPLUS && rate == nullptr)) return QV_ERR_UNSUPPORTED;
   const int by = (N + CG_CHANNELS - 1) / CG_CHANNELS;
   if (by > 65535) return QV_ERR_TOO_LARGE;
   cudaStream_t st = (cudaStream_t)stream;
@@ -101,7 +111,7 @@ extern "C" int qv_channel_gates(float* out, int ld_out, const float* x1, int ld_
   for (int done = 0; done < T; done += per) {
     const int rows = T - done < per ? T - done : per;
     const int rc = qv_launch(channel_gates_kernel, dim3((rows + CG_TOKENS - 1) / CG_TOKENS, by), dim3(4 * CG_CHANNELS), smem, st,
-                             out + (size_t)done * ld_out, ld_out, x1 + (size_t)done * ld_x, ld_x, w2t, bias, rows, N, R, pre_tanh, kind, p);
+                             out + (size_t)done * ld_out, ld_out, x1 + (size_t)done * ld_x, ld_x, w2t, bias, rows, N, R, pre_tanh, kind, p, rate);
     if (rc) return rc;
   }
   return 0;
@@ -139,6 +149,54 @@ extern "C" int qv_unit_keys(float* u, float* au, const float* k, int ld_k, const
     const int rows = T - done < 65535 ? T - done : 65535;
     const int rc = qv_launch(unit_keys_kernel, dim3(rows, (H + 3) / 4), dim3(128), 0, st, u + (size_t)done * H * n,
                              au + (size_t)done * H * n, k + (size_t)done * ld_k, ld_k, a + (size_t)done * ld_a, ld_a, a_bias, H, n, eps);
+    if (rc) return rc;
+  }
+  return 0;
+}
+
+// The operands of the delta rule whose removal reads the decayed state,
+//   S' = diag(g) S,  S = S' + k (beta (v - S'^T k))^T = diag(g) S - (beta k) ((g * k)^T S) + (beta k) v^T,
+// in the scan's terms: w = g, u = g * k, au = beta k and the written key beta k, with k and q unit vectors per head
+// (x / sqrt(sum x^2 + eps)) and q times q_scale.  q, k [T, G * n] float32 (row strides; head h reads group h / (H / G)),
+// b [T, H] the pre-activation of beta = sigmoid(b), g [T, H * n] -> qh, kb, ug dense [T, H * n].  One warp per (token, head).
+__global__ void __launch_bounds__(128) delta_operands_kernel(float* __restrict__ qh, float* __restrict__ kb, float* __restrict__ ug,
+                                                            const float* __restrict__ q, int ld_q, const float* __restrict__ k, int ld_k,
+                                                            const float* __restrict__ b, int ld_b, const float* __restrict__ g, int ld_g,
+                                                            int H, int G, int n, float eps, float q_scale) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (h >= H) return;
+  const int grp = h / (H / G);
+  const float* qr = q + (size_t)t * ld_q + (size_t)grp * n;
+  const float* kr = k + (size_t)t * ld_k + (size_t)grp * n;
+  const float* gr = g + (size_t)t * ld_g + (size_t)h * n;
+  float sq = 0.f, sk = 0.f;
+  for (int i = lane; i < n; i += 32) { sq = fmaf(qr[i], qr[i], sq); sk = fmaf(kr[i], kr[i], sk); }
+  sq = warp_sum(sq);
+  sk = warp_sum(sk);
+  const float iq = q_scale / sqrtf(sq + eps), ik = 1.0f / sqrtf(sk + eps);
+  const float beta = 1.0f / (1.0f + expf(-b[(size_t)t * ld_b + h]));
+  const size_t o = ((size_t)t * H + h) * n;
+  for (int i = lane; i < n; i += 32) {
+    const float kk = kr[i] * ik;
+    qh[o + i] = qr[i] * iq;
+    kb[o + i] = beta * kk;
+    ug[o + i] = gr[i] * kk;
+  }
+}
+
+extern "C" int qv_delta_operands(float* qh, float* kb, float* ug, const float* q, int ld_q, const float* k, int ld_k, const float* b,
+                                 int ld_b, const float* g, int ld_g, int T, int H, int G, int n, float eps, float q_scale, void* stream) {
+  if (T <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || n <= 0) return QV_ERR_UNSUPPORTED;
+  cudaStream_t st = (cudaStream_t)stream;
+  for (int done = 0; done < T; done += 65535) {
+    const int rows = T - done < 65535 ? T - done : 65535;
+    const size_t o = (size_t)done * H * n;
+    const int rc = qv_launch(delta_operands_kernel, dim3(rows, (H + 3) / 4), dim3(128), 0, st, qh + o, kb + o, ug + o,
+                             q + (size_t)done * ld_q, ld_q, k + (size_t)done * ld_k, ld_k, b + (size_t)done * ld_b, ld_b,
+                             g + (size_t)done * ld_g, ld_g, H, G, n, eps, q_scale);
     if (rc) return rc;
   }
   return 0;

@@ -523,20 +523,27 @@ extern "C" int qv_add_vector(float* x, const float* v, int T, int d, void* strea
 }
 
 // ---------------------------------------------------------------- ungated activations
-// out = act(x) elementwise in place or not; kind 0: the square of relu.
+// out = act(x) elementwise in place or not; kind 0: the square of relu, 1: the tanh form of GELU.
 template <typename T>
 __global__ void activation_kernel(T* __restrict__ out, const T* __restrict__ x, size_t n, int kind) {
   pdl_wait();
   pdl_launch_dependents();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
-    const float v = fmaxf(to_f(x[i]), 0.f);
-    out[i] = from_f<T>(v * v);
+    const float z = to_f(x[i]);
+    float r;
+    if (kind == 1) {
+      r = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    } else {
+      const float v = fmaxf(z, 0.f);
+      r = v * v;
+    }
+    out[i] = from_f<T>(r);
   }
 }
 
 extern "C" int qv_activation(void* out, const void* x, long long n, int kind, int dt, void* stream) {
   if (n <= 0) return 0;
-  if (kind != 0) return QV_ERR_UNSUPPORTED;
+  if (kind != 0 && kind != 1) return QV_ERR_UNSUPPORTED;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   QV_DISPATCH_DT(dt, TT, return qv_launch(activation_kernel<TT>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (TT*)out, (const TT*)x, (size_t)n, kind));
   return QV_ERR_UNSUPPORTED;
@@ -711,4 +718,76 @@ extern "C" const char* qv_error_string(int code) {
   if (code == QV_ERR_UNSUPPORTED) return "size or dtype not supported by this kernel";
   if (code == QV_ERR_TOO_LARGE) return "size exceeds what this kernel can hold on chip";
   return cudaGetErrorString((cudaError_t)code);
+}
+
+// ---------------------------------------------------------------- norm on a sublayer's output (post-norm blocks)
+// residual[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w     (float32; y in the compute type or float32, row stride ld_y)
+// cast[t] = residual[t] in the compute type, if cast is given: what the next sublayer's products read.
+// One block per row; the sum's order depends on d alone.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256) post_rmsnorm_add_kernel(float* __restrict__ residual, const TY* __restrict__ y, int ld_y,
+                                                              const float* __restrict__ w, float eps, TO* __restrict__ cast, int d) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const TY* yr = y + (size_t)t * ld_y;
+  float* res = residual + (size_t)t * d;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = to_f(yr[i]); ss = fmaf(v, v, ss); }
+  const float total = block_sum(ss, red);
+  const float sc = 1.0f / sqrtf(total / (float)d + eps);
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    const float x = res[i] + to_f(yr[i]) * sc * w[i];
+    res[i] = x;
+    if (cast) cast[(size_t)t * d + i] = from_f<TO>(x);
+  }
+}
+
+extern "C" int qv_post_rmsnorm_add(float* residual, const void* y, int ld_y, const float* w, float eps, void* cast, int T, int d,
+                                   int y_dt, int cast_dt, void* stream) {
+  if (T <= 0 || d <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+#define LAUNCH_POST(TY, TO) \
+  return qv_launch(post_rmsnorm_add_kernel<TY, TO>, dim3(T), dim3(256), 0, st, residual, (const TY*)y, ld_y, w, eps, (TO*)cast, d)
+  if (y_dt == QV_DT_F32 && cast_dt == QV_DT_F32) LAUNCH_POST(float, float);
+  if (y_dt == QV_DT_BF16 && cast_dt == QV_DT_BF16) LAUNCH_POST(bf16, bf16);
+  if (y_dt == QV_DT_F32 && cast_dt == QV_DT_BF16) LAUNCH_POST(float, bf16);
+  if (y_dt == QV_DT_BF16 && cast_dt == QV_DT_F32) LAUNCH_POST(bf16, float);
+#undef LAUNCH_POST
+  return QV_ERR_UNSUPPORTED;
+}
+
+// ---------------------------------------------------------------- RMS norm of rows that are slices
+// out[t, :n] = in[t, :n] * rsqrt(mean(in[t, :n]^2) + eps) * w (w may be null), rows with strides; float32 arithmetic.
+// One warp per row, four rows a block.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128) rmsnorm_rows_kernel(TO* __restrict__ out, int ld_out, const TI* __restrict__ in, int ld_in,
+                                                          const float* __restrict__ w, float eps, int T, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (t >= T) return;
+  const TI* x = in + (size_t)t * ld_in;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) { const float v = to_f(x[i]); ss = fmaf(v, v, ss); }
+  ss = warp_sum(ss);
+  const float sc = 1.0f / sqrtf(ss / (float)n + eps);
+  TO* o = out + (size_t)t * ld_out;
+  for (int i = lane; i < n; i += 32) o[i] = from_f<TO>(to_f(x[i]) * sc * (w ? w[i] : 1.0f));
+}
+
+extern "C" int qv_rmsnorm_rows(void* out, int ld_out, const void* in, int ld_in, const float* w, float eps, int T, int n, int in_dt,
+                               int out_dt, void* stream) {
+  if (T <= 0 || n <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const dim3 grid((T + 3) / 4);
+#define LAUNCH_ROWS(TI, TO) \
+  return qv_launch(rmsnorm_rows_kernel<TI, TO>, grid, dim3(128), 0, st, (TO*)out, ld_out, (const TI*)in, ld_in, w, eps, T, n)
+  if (in_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_ROWS(float, float);
+  if (in_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_ROWS(bf16, bf16);
+  if (in_dt == QV_DT_F32 && out_dt == QV_DT_BF16) LAUNCH_ROWS(float, bf16);
+  if (in_dt == QV_DT_BF16 && out_dt == QV_DT_F32) LAUNCH_ROWS(bf16, float);
+#undef LAUNCH_ROWS
+  return QV_ERR_UNSUPPORTED;
 }

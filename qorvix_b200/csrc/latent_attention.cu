@@ -8,21 +8,22 @@
 // shared one key/value head whose key row is [c | kr] and whose value row is c, and the head's value
 // matrix is applied to the weighted latent afterwards.  A sigmoid gate multiplies the output.
 //
-// qv_latent_prepare: per token, RMS norm of the latent part of the down projection, interleaved-pair
-//   rotation of the shared key part, write of both into the token's cache row; rotation of every head's
-//   query part in place.
+// qv_latent_prepare: per token, RMS norm of the latent part of the down projection, rotation of the shared
+//   key part (neighbouring pairs or split halves), write of both into the token's cache row; rotation of
+//   every head's query part in place.
 // qv_latent_attention_generic: one warp per (token, head), float32 arithmetic whatever the storage type,
 //   keys in blocks of 32 aligned to absolute positions with a running maximum and sum, so a position's
 //   result depends on the position and the cache only.  Serves the true 32-bit path and every size.
 #include "common.cuh"
 
-// proj[t] = [... q: H * (dn + dr) at q_off ... down: rank + dr at kv_off ...], row stride ld.
-// Rotation: entries (2i, 2i+1) of the first `rot` entries of a rotated part, angle row tok_pos of cos_sin.
+// proj[t] = [... down: rank + dr at kv_off ...], row stride ld; q[t] = H * (dn + dr) entries, row stride ld_q (the queries may
+// be columns of proj or a tensor of their own).  Rotation of the first `rot` entries of a rotated part by the angles of row
+// tok_pos of cos_sin: split_half 0 pairs entries (2i, 2i+1), 1 pairs entries (i, i + rot/2).
 template <typename T>
 __global__ void __launch_bounds__(256) latent_prepare_kernel(
-    T* __restrict__ proj, int ld, int q_off, int kv_off, T* __restrict__ cache, const float* __restrict__ norm_w, float eps,
-    const float2* __restrict__ cos_sin, int table_rows, const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
-    const int* __restrict__ block_table, int max_blocks, int H, int dn, int dr, int rank, int rot, int page) {
+    T* __restrict__ proj, int ld, T* __restrict__ q, int ld_q, int kv_off, T* __restrict__ cache, const float* __restrict__ norm_w,
+    float eps, const float2* __restrict__ cos_sin, int table_rows, const int* __restrict__ tok_pos, const int* __restrict__ tok_seg,
+    const int* __restrict__ block_table, int max_blocks, int H, int dn, int dr, int rank, int rot, int page, int split_half) {
   __shared__ float red[33];
   pdl_wait();
   pdl_launch_dependents();
@@ -40,38 +41,46 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(
   const float sc = 1.0f / sqrtf(total / (float)rank + eps);
   for (int i = threadIdx.x; i < rank; i += blockDim.x) dst[i] = from_f<T>(to_f(lat[i]) * sc * norm_w[i]);
   // the shared rotated key part
+  const int pairs = rot >> 1;
   const T* kr = lat + rank;
   for (int i = threadIdx.x; i < dr; i += blockDim.x) {
     float v = to_f(kr[i]);
     if (i < rot) {
-      const float2 c = cs[i >> 1];
-      const float other = to_f(kr[i ^ 1]);
-      v = (i & 1) ? v * c.x + other * c.y : v * c.x - other * c.y;
+      if (split_half) {
+        const bool first = i < pairs;
+        const float2 c = cs[first ? i : i - pairs];
+        const float other = to_f(kr[first ? i + pairs : i - pairs]);
+        v = first ? v * c.x - other * c.y : v * c.x + other * c.y;
+      } else {
+        const float2 c = cs[i >> 1];
+        const float other = to_f(kr[i ^ 1]);
+        v = (i & 1) ? v * c.x + other * c.y : v * c.x - other * c.y;
+      }
     }
     dst[rank + i] = from_f<T>(v);
   }
   // every head's rotated query part, in place (a pair is handled by one thread)
-  const int pairs = rot >> 1;
+  const int step = split_half ? pairs : 1;
   for (int k = threadIdx.x; k < H * pairs; k += blockDim.x) {
     const int h = k / pairs, i = k - h * pairs;
-    T* qr = row + q_off + (size_t)h * (dn + dr) + dn + 2 * i;
-    const float a = to_f(qr[0]), b = to_f(qr[1]);
+    T* qr = q + (size_t)t * ld_q + (size_t)h * (dn + dr) + dn + (split_half ? i : 2 * i);
+    const float a = to_f(qr[0]), b = to_f(qr[step]);
     const float2 c = cs[i];
     qr[0] = from_f<T>(a * c.x - b * c.y);
-    qr[1] = from_f<T>(b * c.x + a * c.y);
+    qr[step] = from_f<T>(b * c.x + a * c.y);
   }
 }
 
-extern "C" int qv_latent_prepare(void* proj, int ld, int q_off, int kv_off, void* cache, const float* norm_w, float eps,
+extern "C" int qv_latent_prepare(void* proj, int ld, void* q, int ld_q, int kv_off, void* cache, const float* norm_w, float eps,
                                  const float* cos_sin, int table_rows, const int* tok_pos, const int* tok_seg,
                                  const int* block_table, int max_blocks, int T, int H, int dn, int dr, int rank, int rot,
-                                 int page, int dt, void* stream) {
+                                 int page, int split_half, int dt, void* stream) {
   if (T <= 0) return 0;
   if (rot < 0 || rot > dr || (rot & 1) || rank <= 0) return QV_ERR_UNSUPPORTED;
   QV_DISPATCH_DT(dt, TT,
-                 return qv_launch(latent_prepare_kernel<TT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, (TT*)proj, ld, q_off, kv_off,
-                                  (TT*)cache, norm_w, eps, (const float2*)cos_sin, table_rows, tok_pos, tok_seg, block_table,
-                                  max_blocks, H, dn, dr, rank, rot, page));
+                 return qv_launch(latent_prepare_kernel<TT>, dim3(T), dim3(256), 0, (cudaStream_t)stream, (TT*)proj, ld, (TT*)q, ld_q,
+                                  kv_off, (TT*)cache, norm_w, eps, (const float2*)cos_sin, table_rows, tok_pos, tok_seg, block_table,
+                                  max_blocks, H, dn, dr, rank, rot, page, split_half));
   return QV_ERR_UNSUPPORTED;
 }
 

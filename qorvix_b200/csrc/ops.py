@@ -59,11 +59,11 @@ _ARGTYPES = {
     "qv_add_rmsnorm2": [_V, _V, _V, _V, _V, _V, _I, _I, _F, _I, _I, _V],
     "qv_sum2": [_V, _V, _V, _L, _I, _I, _V],
     "qv_softcap": [_V, _L, _F, _V],
-    "qv_latent_prepare": [_V, _I, _I, _I, _V, _V, _F, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
+    "qv_latent_prepare": [_V, _I, _V, _I, _I, _V, _V, _F, _V, _I, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _V],
     "qv_latent_attention_generic": [_V, _I, _V, _I, _V, _I, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _V],
     "qv_latent_tc_workspace_bytes": [_I, _I, _I, _I, _I],
     "qv_latent_attention_tc": [_V, _I, _V, _I, _V, _I, _V, _V, _V, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _V, _V],
-    "qv_conv_state": [_V, _I, _V, _I, _V, _V, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
+    "qv_conv_state": [_V, _I, _V, _I, _V, _V, _V, _L, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _V],
     "qv_linear_scan_state_floats": [_I, _I, _I, _I],
     "qv_linear_scan": [_I, _V, _I, _V, _I, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _V, _V, _F, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
     "qv_gated_group_norm": [_V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _F, _I, _I, _V],
@@ -89,7 +89,11 @@ _ARGTYPES = {
     "qv_sigmoid_gate": [_V, _V, _I, _V, _I, _V, _I, _I, _I, _V],
     "qv_depth_mix": [_V, _V, _V, _L, _V, _I, _V],
     "qv_scale": [_V, _L, _F, _V],
-    "qv_channel_gates": [_V, _I, _V, _I, _V, _V, _I, _I, _I, _I, _I, _F, _V],
+    "qv_channel_gates": [_V, _I, _V, _I, _V, _V, _I, _I, _I, _I, _I, _F, _V, _V],
+    "qv_delta_operands": [_V, _V, _V, _V, _I, _V, _I, _V, _I, _V, _I, _I, _I, _I, _I, _F, _F, _V],
+    "qv_post_rmsnorm_add": [_V, _V, _I, _V, _F, _V, _I, _I, _I, _I, _V],
+    "qv_rmsnorm_rows": [_V, _I, _V, _I, _V, _F, _I, _I, _I, _I, _V],
+    "qv_rot_norm_prepare": [_V, _I, _V, _I, _I, _I, _I, _V, _V, _I, _I, _I, _F, _V, _V, _I, _F, _V, _V, _V, _I, _I, _I, _I, _I, _I, _I, _I, _V],
     "qv_unit_keys": [_V, _V, _V, _I, _V, _I, _V, _I, _I, _I, _F, _V],
     "qv_channel_scan_state_floats": [_I, _I, _I],
     "qv_channel_scan": [_V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _V, _I, _F, _V, _L, _V, _V, _I, _I, _I, _I, _I, _V],
@@ -332,11 +336,11 @@ def add_vector(x, v) -> None:
     _check(_lib("elementwise").qv_add_vector(_ptr(x), _ptr(v), x.shape[0], x.shape[1], _stream()), "add_vector")
 
 
-ACT_RELU2 = 0
+ACT_RELU2, ACT_GELU_TANH = 0, 1
 
 
 def activation(out, x, kind: int = ACT_RELU2) -> None:
-    """out = act(x) elementwise (out may be x); kind ACT_RELU2: the square of relu."""
+    """out = act(x) elementwise (out may be x); kind ACT_RELU2: the square of relu, ACT_GELU_TANH: the tanh form of GELU."""
     _need_cuda(out, x)
     assert out.dtype == x.dtype and out.is_contiguous() and x.is_contiguous() and out.numel() == x.numel()
     _check(_lib("elementwise").qv_activation(_ptr(out), _ptr(x), x.numel(), kind, dt_code(x.dtype), _stream()), "activation")
@@ -411,6 +415,29 @@ def scale(x, s: float) -> None:
     _need_cuda(x)
     assert x.dtype == torch.float32 and x.is_contiguous()
     _check(_lib("elementwise").qv_scale(_ptr(x), x.numel(), float(s), _stream()), "scale")
+
+
+def post_rmsnorm_add(residual, y, weight, eps: float, cast=None) -> None:
+    """residual (float32 [T, d]) += y / rms(y) * weight, the root mean square over a row of y with eps under the root; y in the
+    compute type or float32 (rows may be strided); `cast`, if given, receives the new residual in its own type."""
+    _need_cuda(residual, y, weight, cast)
+    T, d = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous() and tuple(y.shape) == (T, d) and y.stride(1) == 1
+    assert weight.dtype == torch.float32 and weight.numel() == d and (cast is None or (cast.is_contiguous() and cast.shape == residual.shape))
+    rc = _lib("elementwise").qv_post_rmsnorm_add(_ptr(residual), _ptr(y), y.stride(0), _ptr(weight), float(eps), _ptr(cast), T, d,
+                                                 dt_code(y.dtype), dt_code(cast.dtype) if cast is not None else F32, _stream())
+    _check(rc, "post_rmsnorm_add")
+
+
+def rmsnorm_rows(out, x, weight, eps: float) -> None:
+    """out[t] = x[t] / rms(x[t]) * weight (weight float32 or None), rows of either may be column slices; float32 arithmetic."""
+    _need_cuda(out, x, weight)
+    T, n = x.shape
+    assert tuple(out.shape) == (T, n) and out.stride(1) == 1 and x.stride(1) == 1
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == n)
+    rc = _lib("elementwise").qv_rmsnorm_rows(_ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(weight), float(eps), T, n,
+                                             dt_code(x.dtype), dt_code(out.dtype), _stream())
+    _check(rc, "rmsnorm_rows")
 
 
 # ------------------------------------------------------------------ differential attention
@@ -513,19 +540,22 @@ def diff_attention(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, win
 
 # ------------------------------------------------------------------ latent attention
 
-def latent_prepare(proj, q_off: int, kv_off: int, cache_layer, norm_w, eps, cos_sin, ctx, block_table, H, dn, dr, rank, rot, page) -> None:
-    """Per token of proj (rows [.. q: H*(dn+dr) at q_off .. down: rank+dr at kv_off ..]): the latent part of the
-    down projection RMS-normed, the shared key part rotated (pairs 2i, 2i+1), both written to the token's row of
-    cache_layer [pages, page, rank+dr]; every head's rotated query part rotated in place."""
-    _need_cuda(proj, cache_layer, norm_w, cos_sin, block_table)
-    assert proj.stride(1) == 1 and cache_layer.is_contiguous() and cache_layer.dtype == proj.dtype
+def latent_prepare(proj, q, kv_off: int, cache_layer, norm_w, eps, cos_sin, ctx, block_table, H, dn, dr, rank, rot, page,
+                   split_half: bool = False) -> None:
+    """Per token of proj (rows [.. down: rank+dr at kv_off ..]): the latent part of the down projection RMS-normed, the
+    shared key part rotated (pairs 2i, 2i+1, or i, i + rot/2 with split_half), both written to the token's row of
+    cache_layer [pages, page, rank+dr]; every head's rotated query part of q [T, H*(dn+dr)] (columns of proj or a tensor
+    of its own) rotated in place."""
+    _need_cuda(proj, q, cache_layer, norm_w, cos_sin, block_table)
+    assert proj.stride(1) == 1 and cache_layer.is_contiguous() and cache_layer.dtype == proj.dtype == q.dtype
+    assert q.stride(1) == 1 and q.shape[0] == proj.shape[0] and q.shape[1] == H * (dn + dr)
     assert tuple(cache_layer.shape[1:]) == (page, rank + dr) and norm_w.dtype == torch.float32 and norm_w.numel() == rank
     assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] * 2 == rot
     _i32(block_table, "block_table")
     rc = _lib("latent_attention").qv_latent_prepare(
-        _ptr(proj), proj.stride(0), q_off, kv_off, _ptr(cache_layer), _ptr(norm_w), eps, _ptr(cos_sin), cos_sin.shape[0],
+        _ptr(proj), proj.stride(0), _ptr(q), q.stride(0), kv_off, _ptr(cache_layer), _ptr(norm_w), eps, _ptr(cos_sin), cos_sin.shape[0],
         _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table), block_table.shape[-1], proj.shape[0], H, dn, dr, rank, rot, page,
-        dt_code(proj.dtype), _stream())
+        1 if split_half else 0, dt_code(proj.dtype), _stream())
     _check(rc, "latent_prepare")
 
 
@@ -597,19 +627,21 @@ def latent_attention(out, q, gate, cache_layer, wuk, wuv, ctx, block_table, H, d
 SCAN_GATED_MAX, SCAN_DECAY = 0, 1
 
 
-def conv_state(out, x, w, bias, tail, ctx) -> None:
-    """out = silu(causal convolution of x along each request's tokens + bias), per channel; w [channels, taps]
-    float32 with the current token's tap last; tail [slots, (taps-1)*channels] float32 keeps each request's
-    last inputs and is brought up to date."""
+def conv_state(out, x, w, bias, tail, ctx, act: bool = True, add_input: bool = False) -> None:
+    """out = f(causal convolution of x along each request's tokens + bias), per channel, f SiLU or (act False) the
+    identity; with add_input the current input is added (out = x + f(conv)); w [channels, taps] float32 with the
+    current token's tap last; tail [slots, (taps-1)*channels] float32 keeps each request's last inputs and is brought
+    up to date.  x and out may differ in type (float32 or bfloat16 each)."""
     _need_cuda(out, x, w, bias, tail)
     T, C = x.shape
-    assert out.shape == x.shape and out.dtype == x.dtype and out.stride(1) == 1 and x.stride(1) == 1
+    assert out.shape == x.shape and out.stride(1) == 1 and x.stride(1) == 1
     assert w.dtype == torch.float32 and w.is_contiguous() and w.shape[0] == C and tail.dtype == torch.float32
     taps = w.shape[1]
     assert tail.stride(-1) == 1 and tail.shape[-1] >= (taps - 1) * C
     rc = _lib("recurrent").qv_conv_state(
         _ptr(out), out.stride(0), _ptr(x), x.stride(0), _ptr(w), _ptr(bias), _ptr(tail), tail.stride(0), _ptr(ctx.seg_q_start),
-        _ptr(ctx.seg_slot), ctx.num_segments, ctx.max_q_len, C, taps, dt_code(x.dtype), _stream())
+        _ptr(ctx.seg_slot), ctx.num_segments, ctx.max_q_len, C, taps, dt_code(x.dtype), dt_code(out.dtype), 1 if act else 0,
+        1 if add_input else 0, _stream())
     _check(rc, "conv_state")
 
 
@@ -650,22 +682,39 @@ def gated_group_norm(out, y, gate, w, groups: int, eps: float, gate_first: bool)
 
 # ------------------------------------------------------------------ recurrences with a decay per key channel
 
-GATE_POW_SIGMOID, GATE_EXP_NEG_SIGMOID = 0, 1
+GATE_POW_SIGMOID, GATE_EXP_NEG_SIGMOID, GATE_EXP_NEG_SOFTPLUS, GATE_LINEAR = 0, 1, 2, 3
 HEAD_GATE_SIGMOID, HEAD_GATE_SILU = 0, 1
 
 
-def channel_gates(out, x1, w2t, bias, pre_tanh: bool, kind: int, p: float) -> None:
+def channel_gates(out, x1, w2t, bias, pre_tanh: bool, kind: int, p: float, rate=None) -> None:
     """out[t, c] (float32) = g(sum_r f(x1[t, r]) w2t[r, c] + bias[c]): f the identity or tanh; g(z) = sigmoid(z)^p
-    (GATE_POW_SIGMOID) or exp(-p sigmoid(z)) (GATE_EXP_NEG_SIGMOID).  x1 float32 [T, R] (a column slice is fine),
-    w2t float32 [R, N]: the up matrix transposed, so that neighbouring channels lie side by side."""
-    _need_cuda(out, x1, w2t, bias)
+    (GATE_POW_SIGMOID), exp(-p sigmoid(z)) (GATE_EXP_NEG_SIGMOID), exp(-rate[c] softplus(z)) (GATE_EXP_NEG_SOFTPLUS, rate
+    float32 [N]) or z (GATE_LINEAR).  x1 float32 [T, R] (a column slice is fine), w2t float32 [R, N]: the up matrix
+    transposed, so that neighbouring channels lie side by side."""
+    _need_cuda(out, x1, w2t, bias, rate)
+    assert rate is None or (rate.dtype == torch.float32 and rate.is_contiguous() and rate.numel() == w2t.shape[1])
     T, R = x1.shape
     N = w2t.shape[1]
     assert out.dtype == x1.dtype == w2t.dtype == torch.float32 and out.stride(1) == 1 and x1.stride(1) == 1 and w2t.is_contiguous()
     assert tuple(out.shape) == (T, N) and w2t.shape[0] == R and (bias is None or (bias.dtype == torch.float32 and bias.numel() == N))
     rc = _lib("channel_scan").qv_channel_gates(_ptr(out), out.stride(0), _ptr(x1), x1.stride(0), _ptr(w2t), _ptr(bias), T, N, R,
-                                               1 if pre_tanh else 0, kind, float(p), _stream())
+                                               1 if pre_tanh else 0, kind, float(p), _ptr(rate), _stream())
     _check(rc, "channel_gates")
+
+
+def delta_operands(qh, kb, ug, q, k, b, g, H: int, G: int, n: int, eps: float, q_scale: float) -> None:
+    """The scan's operands for a delta rule whose removal reads the decayed state: per token and head (head h reads group
+    h // (H // G) of q and k) qh = q / |q| * q_scale, kb = sigmoid(b) k / |k|, ug = g * k / |k|, |x| = sqrt(sum x^2 + eps); q, k
+    float32 [T, G*n], b float32 [T, H], g float32 [T, H*n] (column slices are fine); qh, kb, ug dense float32 [T, H*n]."""
+    _need_cuda(qh, kb, ug, q, k, b, g)
+    T = q.shape[0]
+    for x in (qh, kb, ug):
+        assert x.dtype == torch.float32 and x.is_contiguous() and tuple(x.shape) == (T, H * n)
+    for x in (q, k, b, g):
+        assert x.dtype == torch.float32 and x.stride(1) == 1 and x.shape[0] == T
+    rc = _lib("channel_scan").qv_delta_operands(_ptr(qh), _ptr(kb), _ptr(ug), _ptr(q), q.stride(0), _ptr(k), k.stride(0), _ptr(b), b.stride(0),
+                                                _ptr(g), g.stride(0), T, H, G, n, float(eps), float(q_scale), _stream())
+    _check(rc, "delta_operands")
 
 
 def unit_keys(u, au, k, a, a_bias, H: int, n: int, eps: float) -> None:
@@ -732,6 +781,29 @@ def bias_attn_prepare(q_out, proj, q_off, k_off, v_off, bq, bk, bv, cache_layer,
     _check(rc, "bias_attn_prepare")
 
 
+def rot_norm_prepare(q_out, proj, q_off, k_off, v_off, cache_layer, cos_sin, rot, unit, eps, head_temp, v_first, lam, ctx, block_table,
+                     H, G, n, dv, page) -> None:
+    """From a float32 product's row [.. q .. k .. v ..]: q and k heads rotated over their first `rot` entries (pairs i, i + rot/2,
+    cos_sin [rows, rot/2, 2] float32), then, with `unit`, divided by their root mean square (eps under the root); q times
+    head_temp[h] (float32 [H] or None) -> q_out (compute type); v, blended as (1 - lam) v + lam v_first[t] where v_first (float32
+    [T, G*dv], a column slice is fine) is given, and k go into the token's cache row [G*n | G*dv]."""
+    _need_cuda(q_out, proj, cache_layer, cos_sin, head_temp, v_first, block_table)
+    T = proj.shape[0]
+    assert proj.dtype == torch.float32 and proj.stride(1) == 1 and q_out.stride(1) == 1 and q_out.dtype == cache_layer.dtype
+    assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (n + dv))
+    assert head_temp is None or (head_temp.dtype == torch.float32 and head_temp.numel() == H)
+    assert v_first is None or (v_first.dtype == torch.float32 and v_first.stride(1) == 1 and tuple(v_first.shape) == (T, G * dv))
+    if rot:
+        assert cos_sin.dtype == torch.float32 and cos_sin.is_contiguous() and cos_sin.shape[1] * 2 == rot
+    _i32(block_table, "block_table")
+    rc = _lib("bias_attention").qv_rot_norm_prepare(
+        _ptr(q_out), q_out.stride(0), _ptr(proj), proj.stride(0), q_off, k_off, v_off, _ptr(cache_layer), _ptr(cos_sin) if rot else None,
+        cos_sin.shape[0] if rot else 1, int(rot), 1 if unit else 0, float(eps), _ptr(head_temp), _ptr(v_first),
+        v_first.stride(0) if v_first is not None else 0, float(lam), _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table),
+        block_table.shape[-1], T, H, G, n, dv, page, dt_code(q_out.dtype), _stream())
+    _check(rc, "rot_norm_prepare")
+
+
 def bias_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, page, scale, bucket, bias, gate, factor) -> None:
     """out[t, h] = softmax_j((q_t,h . k_j) * scale + bias[bucket[min(i - j, len(bucket) - 1)], h]) v_j over the request's pages,
     times sigmoid(gate[t, h]) (float32, or None) and factor."""
@@ -739,12 +811,14 @@ def bias_attention_generic(out, q, cache_layer, ctx, block_table, H, G, n, dv, p
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == out.dtype == cache_layer.dtype
     assert cache_layer.is_contiguous() and tuple(cache_layer.shape[1:]) == (page, G * (n + dv))
-    assert bucket.dtype == torch.int32 and bucket.is_contiguous() and bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[1] == H
+    assert (bias is None) == (bucket is None), "a bias table comes with the buckets of its distances"
+    if bias is not None:
+        assert bucket.dtype == torch.int32 and bucket.is_contiguous() and bias.dtype == torch.float32 and bias.is_contiguous() and bias.shape[1] == H
     assert gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1)
     _i32(block_table, "block_table")
     rc = _lib("bias_attention").qv_bias_attention_generic(
         _ptr(out), out.stride(0), _ptr(q), q.stride(0), _ptr(cache_layer), _ptr(ctx.tok_pos), _ptr(ctx.tok_seg), _ptr(block_table),
-        block_table.shape[-1], T, H, G, n, dv, page, float(scale), _ptr(bucket), bucket.numel() - 1, _ptr(bias), _ptr(gate),
+        block_table.shape[-1], T, H, G, n, dv, page, float(scale), _ptr(bucket), bucket.numel() - 1 if bucket is not None else 0, _ptr(bias), _ptr(gate),
         gate.stride(0) if gate is not None else 0, float(factor), dt_code(q.dtype), _stream())
     _check(rc, "bias_attention_generic")
 

@@ -1,7 +1,8 @@
 // Recurrent mixers' kernels: a per-request state of fixed size carried from token to token.
 //
-// qv_conv_state     short causal convolution per channel with bias and SiLU, the last taps-1 inputs of a
-//                   request kept as state so that a portion continues where the last one ended.
+// qv_conv_state     short causal convolution per channel with optional bias, optional SiLU and optionally the input
+//                   added to the result, the last taps-1 inputs of a request kept as state so that a portion continues
+//                   where the last one ended.
 // qv_linear_scan    S_t = a_t S_(t-1) + b_t k_t v_t^T;  y_t = S_t^T q_t  per head, S in float32, in two kinds:
 //                     GATED_MAX  exponential gates stabilised by a running maximum (matrix-memory LSTM):
 //                                log i = cap tanh((gi + bi)/cap), log f = logsigmoid(cap tanh((gf + bf)/cap)),
@@ -17,14 +18,16 @@
 #define CONV_MAX_TAPS 16
 #define CONV_CHUNK 64
 
-// in/out: [T, channels] with row strides; w [channels, taps] (last column: the current token), bias [channels];
-// tail [slots][(taps-1) * channels] float32, oldest input first.  grid (segments, channel tiles, time chunks).
-template <typename T>
-__global__ void __launch_bounds__(128) conv_state_kernel(T* __restrict__ out, int ld_out, const T* __restrict__ in, int ld_in,
+// in/out: [T, channels] with row strides and types of their own; w [channels, taps] (last column: the current token),
+// bias [channels] or null; tail [slots][(taps-1) * channels] float32, oldest input first.  act 1: SiLU of the sum, 0: the sum
+// as it is; add_input 1: the current input is added to the result (out = in + conv(in), after the activation).
+// grid (segments, channel tiles, time chunks).
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128) conv_state_kernel(TO* __restrict__ out, int ld_out, const TI* __restrict__ in, int ld_in,
                                                          const float* __restrict__ w, const float* __restrict__ bias,
                                                          float* __restrict__ tail, long long slot_stride,
                                                          const int* __restrict__ seg_q_start, const int* __restrict__ seg_slot,
-                                                         int channels, int taps) {
+                                                         int channels, int taps, int act, int add_input) {
   pdl_wait();
   pdl_launch_dependents();
   const int s = blockIdx.x;
@@ -43,16 +46,19 @@ __global__ void __launch_bounds__(128) conv_state_kernel(T* __restrict__ out, in
   const float b = bias ? bias[c] : 0.f;
   // a chunk is at least as long as the longest filter, so only the first chunk reaches back into the state
   for (int j = j0; j < j1; ++j) {
-    float acc = b;
+    float acc = b, cur = 0.f;
 #pragma unroll
     for (int i = 0; i < CONV_MAX_TAPS; ++i) {
       if (i < taps) {
         const int idx = j - (taps - 1) + i;
         const float v = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : old[taps - 1 + idx];
         acc = fmaf(wt[i], v, acc);
+        if (i == taps - 1) cur = v;
       }
     }
-    out[(size_t)(q0 + j) * ld_out + c] = from_f<T>(acc / (1.0f + expf(-acc)));
+    if (act) acc = acc / (1.0f + expf(-acc));
+    if (add_input) acc += cur;
+    out[(size_t)(q0 + j) * ld_out + c] = from_f<TO>(acc);
   }
   if (blockIdx.z == 0) {
     for (int i = 0; i < taps - 1; ++i) {
@@ -64,15 +70,20 @@ __global__ void __launch_bounds__(128) conv_state_kernel(T* __restrict__ out, in
 
 extern "C" int qv_conv_state(void* out, int ld_out, const void* in, int ld_in, const float* w, const float* bias, float* tail,
                              long long slot_stride, const int* seg_q_start, const int* seg_slot, int S, int max_q_len,
-                             int channels, int taps, int dt, void* stream) {
+                             int channels, int taps, int in_dt, int out_dt, int act, int add_input, void* stream) {
   if (S <= 0 || channels <= 0) return 0;
   if (taps < 1 || taps > CONV_MAX_TAPS) return QV_ERR_UNSUPPORTED;
   const int chunks = max_q_len > 0 ? (max_q_len + CONV_CHUNK - 1) / CONV_CHUNK : 1;
   if (chunks > 65535 || (channels + 127) / 128 > 65535) return QV_ERR_TOO_LARGE;
   dim3 grid(S, (channels + 127) / 128, chunks);
-  QV_DISPATCH_DT(dt, TT,
-                 return qv_launch(conv_state_kernel<TT>, grid, dim3(128), 0, (cudaStream_t)stream, (TT*)out, ld_out, (const TT*)in,
-                                  ld_in, w, bias, tail, slot_stride, seg_q_start, seg_slot, channels, taps));
+#define LAUNCH_CONV(TI, TO)                                                                                                    \
+  return qv_launch(conv_state_kernel<TI, TO>, grid, dim3(128), 0, (cudaStream_t)stream, (TO*)out, ld_out, (const TI*)in, ld_in, w, \
+                   bias, tail, slot_stride, seg_q_start, seg_slot, channels, taps, act, add_input)
+  if (in_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_CONV(float, float);
+  if (in_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_CONV(bf16, bf16);
+  if (in_dt == QV_DT_F32 && out_dt == QV_DT_BF16) LAUNCH_CONV(float, bf16);
+  if (in_dt == QV_DT_BF16 && out_dt == QV_DT_F32) LAUNCH_CONV(bf16, float);
+#undef LAUNCH_CONV
   return QV_ERR_UNSUPPORTED;
 }
 

@@ -46,6 +46,7 @@ class StepContext:
     max_ctx_len: int = 0
     captured: bool = False             # the step is being captured or replayed as a CUDA graph
     next_norm: object = None           # set by the model before each block: the norm the block after it starts with
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)    # what a layer leaves for later layers of the same step
 
     @property
     def decode_only(self) -> bool:

@@ -1,7 +1,7 @@
 """Block arrangements.  'pre_norm' is the reference's (runtime/src/text_model.cpp:146-168):
     x += mixer(norm(x));  x += feed_forward(norm(x))
 The residual stream is float32.  A block hands the feed-forward's output on as a pending
-delta, which the next norm adds in its own pass."""
+delta, which the next norm adds in its own pass.  'post_norm' puts the norms on the parts' outputs instead."""
 from __future__ import annotations
 
 import torch
@@ -177,6 +177,50 @@ class GatedPreNormBlock(Block):
         return None                              # its norms do not fold into products
 
 
+class PostNormBlock(Block):
+    """x += norm_a(mixer(x));  x += norm_b(feed_forward(x)): the parts read the stream itself and the norms sit on their
+    outputs, so the stream is always whole (nothing is pending behind this block).  A norm here offers
+    add_normed(residual, y, cast): the float32 stream takes the normed output and, where a product reads the stream next,
+    leaves in the compute type in the same pass.  A mixer that declares takes_stream reads the float32 stream (its own
+    first pass turns it into the compute type); any other part reads the stream's copy in the compute type."""
+
+    def __init__(self, spec, source, rt):
+        self.rt = rt
+        self.mixer = build_part("mixer", spec.mixer, source, rt)
+        self.mixer_norm = build_part("norm", spec.mixer_norm, source, rt) if self.mixer is not None else None
+        self.feed_forward = build_part("feed_forward", spec.feed_forward, source, rt)
+        self.ffn_norm = build_part("norm", spec.ffn_norm, source, rt) if self.feed_forward is not None else None
+        for norm in (self.mixer_norm, self.ffn_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("a post-norm block needs norms that can be added to the stream (add_normed)")
+
+    def _compute_copy(self, residual):
+        if self.rt.dtype == torch.float32:
+            return residual
+        x = torch.empty(residual.shape, device=residual.device, dtype=self.rt.dtype)
+        ops.cast_rows(x, residual)
+        return x
+
+    def forward(self, residual, pending, ctx, cache):
+        if pending is not None and not isinstance(pending, PreNormed):       # left by a block of another kind
+            ops.sum2(residual, residual, pending.contiguous())
+        x = None                                    # the stream in the compute type, where a pass already left it
+        if self.mixer is not None:
+            h = residual if getattr(self.mixer, "takes_stream", False) else self._compute_copy(residual)
+            y = self.mixer.forward(h, ctx, cache)
+            if self.feed_forward is not None and self.rt.dtype != torch.float32:
+                x = torch.empty(residual.shape, device=residual.device, dtype=self.rt.dtype)
+            self.mixer_norm.add_normed(residual, y, cast=x)
+        if self.feed_forward is not None:
+            y = self.feed_forward.forward(x if x is not None else self._compute_copy(residual), ctx)
+            self.ffn_norm.add_normed(residual, y)
+        return residual, None
+
+    def first_norm(self):
+        return None                              # no norm reads the stream
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "post_norm", PostNormBlock)
 register_part("block", "gated_pre_norm", GatedPreNormBlock)
 register_part("block", "parallel", ParallelBlock)

@@ -62,18 +62,21 @@ class SwiGLU(FeedForward):
 
 
 class ActMLP(FeedForward):
-    """Ungated feed-forward: down(act(up x)), the activation (the square of relu) as a pass of its own."""
+    """Ungated feed-forward: down(act(up x)), the activation (the square of relu, or the tanh form of GELU) as a pass of
+    its own."""
 
     def __init__(self, spec, source, rt):
-        if spec.activation != "relu2":
-            raise ValueError(f"unknown activation '{spec.activation}' (known: relu2)")
+        acts = {"relu2": ops.ACT_RELU2, "gelu_tanh": ops.ACT_GELU_TANH}
+        if spec.activation not in acts:
+            raise ValueError(f"unknown activation '{spec.activation}' (known: {', '.join(acts)})")
+        self.act = acts[spec.activation]
         self.rt = rt
         self.up = Linear(source.get(spec.up_proj))
         self.down = Linear(source.get(spec.down_proj))
 
     def forward(self, x, ctx):
         act = self.up(x, out_dtype=self.rt.dtype)
-        ops.activation(act, act, ops.ACT_RELU2)
+        ops.activation(act, act, self.act)
         return self.down(act, out_dtype=self.rt.dtype)
 
 

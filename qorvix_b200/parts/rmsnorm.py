@@ -1,5 +1,6 @@
 """RMSNorm: out = (x * 1/sqrt(mean(x^2) + eps)) * w, no bias (reference: runtime/src/ops.cpp:8-13); a spec
-with `one_plus` stores its weight around zero and the rows are scaled by 1 + w (formed once, in float32).  The residual sum that precedes it is fused in: the
+with `one_plus` stores its weight around zero and the rows are scaled by 1 + w (formed once, in float32); a spec with
+`scalar` stores one number for all coordinates.  The residual sum that precedes it is fused in: the
 residual stream is float32 and the delta is added in float32 in the same pass."""
 from __future__ import annotations
 
@@ -15,6 +16,8 @@ class RMSNorm(Norm):
         self.eps = float(spec.eps)
         self.size = int(spec.size)
         self.weight = source.get(spec.weight, dtype=torch.float32)   # tiny; always read as float32
+        if getattr(spec, "scalar", False):                           # one number for all coordinates
+            self.weight = self.weight.reshape(1).expand(self.size).contiguous()
         if getattr(spec, "one_plus", False):
             self.weight = (self.weight.double() + 1.0).float()       # exact: a bfloat16 value plus one fits float32's 24 bits or rounds once
         self.rt = rt
@@ -33,6 +36,12 @@ class RMSNorm(Norm):
         out = torch.empty((n, self.size), device=residual.device, dtype=self.rt.dtype)
         ops.add_rmsnorm(out, residual, delta, self.weight, self.eps, row_idx=rows)
         return out
+
+
+    def add_normed(self, residual, y, cast=None):
+        """residual (float32) += rmsnorm(y) * weight: the norm on a sublayer's output (post-norm blocks).  `cast`, if
+        given, receives the new stream in the compute type."""
+        ops.post_rmsnorm_add(residual, y, self.weight, self.eps, cast=cast)
 
 
 register_part("norm", "rmsnorm", RMSNorm)

@@ -47,9 +47,10 @@ class RMSNormSpec:
     weight: str
     kind: str = "rmsnorm"
     one_plus: bool = False                    # the stored weight lies around zero: the rows are scaled by 1 + w
+    scalar: bool = False                      # the stored weight is one number for all coordinates
 
     def tensors(self) -> TensorTable:
-        return {self.weight: ((self.size,), "normal:0:0.1" if self.one_plus else "norm")}
+        return {self.weight: (() if self.scalar else (self.size,), "normal:0:0.1" if self.one_plus else "norm")}
 
 
 @dataclass(frozen=True)
@@ -119,7 +120,9 @@ class BigramEmbeddingSpec:
 class LatentAttentionSpec:
     """Causal attention whose keys and values are expanded from a cached low-rank latent; each head's
     query and key have `head_dim` unrotated entries followed by `rot_dim` rotated ones, the rotated key
-    part being one vector shared by all heads; a sigmoid gate multiplies the heads' outputs."""
+    part being one vector shared by all heads; optionally a sigmoid gate multiplies the heads' outputs
+    (gate_proj), and optionally the queries pass a latent of their own: c = rmsnorm(q_down x) * q_norm,
+    q = q_proj c with q_proj [heads * (head_dim + rot_dim), q_rank]."""
     hidden_size: int
     num_heads: int
     head_dim: int                 # unrotated query/key entries per head
@@ -127,27 +130,37 @@ class LatentAttentionSpec:
     value_dim: int
     kv_rank: int
     scale: float
-    eps: float                    # of the latent's RMS norm
-    position: object              # RotarySpec over rot_dim with interleaved pairing
+    eps: float                    # of the latents' RMS norms
+    position: object              # RotarySpec over rot_dim; pairing 'interleaved' or 'split_half'
     q_proj: str
     kv_down: str                  # [kv_rank + rot_dim, hidden]
     kv_norm: str
     k_up: str                     # [heads * head_dim, kv_rank]
     v_up: str                     # [heads * value_dim, kv_rank]
-    gate_proj: str
+    gate_proj: Optional[str]
     o_proj: str
     window: int = 0
     kind: str = "latent_attention"
+    q_rank: int = 0               # > 0: the queries' latent size
+    q_down: Optional[str] = None  # [q_rank, hidden]
+    q_norm: Optional[str] = None  # [q_rank]
 
     def tensors(self) -> TensorTable:
         H, d = self.num_heads, self.hidden_size
-        return {self.q_proj: ((H * (self.head_dim + self.rot_dim), d), "matrix"),
-                self.kv_down: ((self.kv_rank + self.rot_dim, d), "matrix"),
-                self.kv_norm: ((self.kv_rank,), "norm"),
-                self.k_up: ((H * self.head_dim, self.kv_rank), "matrix"),
-                self.v_up: ((H * self.value_dim, self.kv_rank), "matrix"),
-                self.gate_proj: ((H * self.value_dim, d), "matrix"),
-                self.o_proj: ((d, H * self.value_dim), "matrix")}
+        t = {self.kv_down: ((self.kv_rank + self.rot_dim, d), "matrix"),
+             self.kv_norm: ((self.kv_rank,), "norm"),
+             self.k_up: ((H * self.head_dim, self.kv_rank), "matrix"),
+             self.v_up: ((H * self.value_dim, self.kv_rank), "matrix"),
+             self.o_proj: ((d, H * self.value_dim), "matrix")}
+        if self.q_rank:
+            t[self.q_down] = ((self.q_rank, d), "matrix")
+            t[self.q_norm] = ((self.q_rank,), "norm")
+            t[self.q_proj] = ((H * (self.head_dim + self.rot_dim), self.q_rank), "matrix")
+        else:
+            t[self.q_proj] = ((H * (self.head_dim + self.rot_dim), d), "matrix")
+        if self.gate_proj is not None:
+            t[self.gate_proj] = ((H * self.value_dim, d), "matrix")
+        return t
 
 
 @dataclass(frozen=True)
@@ -299,7 +312,7 @@ class DiffAttentionSpec:
 
 @dataclass(frozen=True)
 class ActMLPSpec:
-    """Ungated feed-forward: down(act(up x)), no biases; act 'relu2' is the square of relu."""
+    """Ungated feed-forward: down(act(up x)), no biases; act 'relu2' is the square of relu, 'gelu_tanh' the tanh form of GELU."""
     hidden_size: int
     intermediate_size: int
     up_proj: str
@@ -501,6 +514,107 @@ class BiasedAttentionSpec:
 
 
 @dataclass(frozen=True)
+class RotNormAttentionSpec:
+    """Causal grouped-query softmax attention whose queries and keys are rotated over their first rotary_dim entries
+    (`position`, a RotarySpec in split halves, or None) and then divided by their root mean square over the head (no
+    weight; eps under the root); the score is (q . k) * scale * head_temp[h] (head_temp: a number per head, or None).
+    Key and value sizes are unrelated.  Values may be shared between layers: the layer with v_share_role 'source'
+    publishes its values of the step's tokens under the name v_share, a layer with role 'blend' replaces its values
+    by (1 - lam) v + lam v_source before they are cached, lam being the number stored as v_blend."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    head_dim: int
+    value_dim: int
+    scale: float
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    o_proj: str
+    position: Optional[object] = None
+    head_temp: Optional[str] = None
+    v_share: Optional[str] = None
+    v_share_role: Optional[str] = None        # 'source' | 'blend' | None
+    v_blend: Optional[str] = None             # a number; stored in every sharing layer, used by 'blend' layers
+    kind: str = "rot_norm_attention"
+
+    def tensors(self) -> TensorTable:
+        H, G, n, dv, d = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.hidden_size
+        t: TensorTable = {self.q_proj: ((H * n, d), "matrix"), self.k_proj: ((G * n, d), "matrix"), self.v_proj: ((G * dv, d), "matrix"),
+                          self.o_proj: ((d, H * dv), "matrix")}
+        if self.head_temp is not None:
+            t[self.head_temp] = ((H,), "normal:1:0.2")
+        if self.v_blend is not None:
+            t[self.v_blend] = ((), "normal:0.4:0.1")
+        if self.position is not None:
+            t.update(self.position.tensors())
+        return t
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """Delta rule with a decay per head and key channel whose removal reads the decayed state.  Per head (head h reads
+    query/key group h // (heads / kv_heads)): S <- diag(g) S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q.
+    q, k, v pass a short causal convolution per channel (<name>.conv, [channels, taps], the current token's tap last) and SiLU;
+    q and k are then unit vectors per head (key_eps under the root), q times key_dim^(-1/2); beta = sigmoid(W_b x);
+    g = exp(-exp(a_log[h]) softplus(W_a2 W_a1 x + dt_bias)); o is divided by its root mean square per head, weighted
+    (norm, [value_dim], shared by the heads) and multiplied by sigmoid(W_g2 W_g1 x)."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    decay_rank: int               # rows of a_down
+    gate_rank: int                # rows of gate_down
+    eps: float
+    q_proj: str
+    k_proj: str
+    v_proj: str
+    beta_proj: str
+    a_down: str
+    a_up: str
+    dt_bias: str
+    a_log: str
+    gate_down: str
+    gate_up: str
+    norm: str
+    o_proj: str
+    key_eps: float = 1e-6
+    kind: str = "channel_delta"
+
+    def tensors(self) -> TensorTable:
+        H, G, dk, dv, d = self.num_heads, self.num_kv_heads, self.key_dim, self.value_dim, self.hidden_size
+        t: TensorTable = {self.q_proj: ((G * dk, d), "matrix"), self.k_proj: ((G * dk, d), "matrix"), self.v_proj: ((H * dv, d), "matrix"),
+                          self.beta_proj: ((H, d), "matrix"), self.a_down: ((self.decay_rank, d), "matrix"),
+                          self.a_up: ((H * dk, self.decay_rank), "normal:0:0.3"), self.dt_bias: ((H * dk,), "normal:-1:1"),
+                          self.a_log: ((H,), "normal:-1:0.5"), self.gate_down: ((self.gate_rank, d), "matrix"),
+                          self.gate_up: ((H * dv, self.gate_rank), "normal:0:0.3"), self.norm: ((dv,), "norm"),
+                          self.o_proj: ((d, H * dv), "matrix")}
+        for name, ch in ((self.q_proj, G * dk), (self.k_proj, G * dk), (self.v_proj, H * dv)):
+            t[name + ".conv"] = ((ch, self.conv_taps), "normal:0:0.4")
+        return t
+
+
+@dataclass(frozen=True)
+class ConvInputSpec:
+    """A mixer whose input h first becomes h + conv(h), a causal convolution over time per channel without bias or activation
+    (weight [hidden, taps], the current token's tap last, zeros before a sequence's start); the last taps - 1 inputs are
+    part of the request's state."""
+    inner: object
+    hidden_size: int
+    taps: int
+    weight: str
+    kind: str = "conv_input"
+
+    def tensors(self) -> TensorTable:
+        t = dict(self.inner.tensors())
+        t[self.weight] = ((self.hidden_size, self.taps), "normal:0:0.3")
+        return t
+
+
+@dataclass(frozen=True)
 class SideBySideSpec:
     """Two mixers that read the same input; the result is left_scale * left + right_scale * right."""
     left: object
@@ -536,7 +650,9 @@ class LayerSpec:
     mixer_scale / ffn_scale name per-feature factors of the two parts' outputs ("layer scale") and
     residual_mult multiplies what the block adds to the stream; the parallel block applies them.
     'gated_pre_norm' is 'pre_norm' with each part's output multiplied by sigmoid(W h + b), h being the part's input:
-    mixer_gate / ffn_gate name W [width, width], the bias is name + ".b"."""
+    mixer_gate / ffn_gate name W [width, width], the bias is name + ".b".
+    'post_norm': x += mixer_norm(mixer(x)); x += ffn_norm(feed_forward(x)): the parts read the stream itself and the norms
+    sit on their outputs."""
     mixer: object
     feed_forward: object
     mixer_norm: object
