@@ -189,7 +189,7 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=2048)
     ap.add_argument("--skip-points", action="store_true", help="only the headline shape: no batch 1/64, no other shapes, no kernels")
     ap.add_argument("--shape", default="llama31_8b", choices=sorted(SHAPES), help="the headline shape")
-    ap.add_argument("--design", default="", choices=["", "deganex", "lotirax", "tubazen"],
+    ap.add_argument("--design", default="", choices=["", "deganex", "lotirax", "tubazen", "lugizen"],
                     help="instead of the headline workload: prefill and decode of this design at real layer sizes beside the Llama "
                          "decoder of equal size, and its kernels alone (qorvix_b200/design_bench.py)")
     ap.add_argument("--layers-per-kind", type=int, default=2, help="--design: layers of each kind of mixer")

@@ -1,9 +1,9 @@
-"""Prefill and decode throughput of a Deganex, a Lotirax or a Tubazen model at layer sizes that resemble real models, beside the
+"""Prefill and decode throughput of a Deganex, a Lotirax, a Tubazen or a Lugizen model at layer sizes that resemble real models, beside the
 Llama decoder at equal width, depth and (active) feed-forward size, and the design's kernels alone with their roofline
 fractions beside the Llama kernels they correspond to.
 
-    python bench.py --design deganex|lotirax|tubazen [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
-    python -m qorvix_b200.design_bench [--design lotirax|tubazen]
+    python bench.py --design deganex|lotirax|tubazen|lugizen [--layers-per-kind 2] [--batch 8] [--ctx 1024] [--prefill-tokens 2048]
+    python -m qorvix_b200.design_bench [--design lotirax|tubazen|lugizen]
 
 Random bfloat16 weights; timing with CUDA events after warm-up; kernels alone are timed in captured chains over
 buffers larger than L2 (kernel_bench.timed_chain).  Figures go out as one JSON line.
@@ -116,8 +116,9 @@ def _ctx(seg_lens, pos0, device="cuda"):
         tok_pos=torch.cat([torch.arange(p, p + n, **i32) for p, n in zip(pos0, seg_lens)]))
 
 
-def latent_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
-    """Latent attention of the given segments, each ending at ctx_len cached tokens (prepare excluded)."""
+def latent_attention_case(seg_lens, ctx_len, peaks, page=16, window=0, gated=True) -> dict:
+    """Latent attention of the given segments, each ending at ctx_len cached tokens (prepare excluded); window > 0: the last
+    `window` keys only; gated False: without the output gate."""
     H, dn, dr, dv, rank = ATTN["heads"], ATTN["dim"], ATTN["rot_dim"], ATTN["vdim"], ATTN["kv_rank"]
     S, T = len(seg_lens), sum(seg_lens)
     blocks = -(-ctx_len // page)
@@ -129,16 +130,18 @@ def latent_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
     ctx.seg_len, ctx.seg_start_pos, ctx.max_ctx_len, ctx.captured = list(seg_lens), [ctx_len - n for n in seg_lens], ctx_len, False
     ctx.seg_pos0 = torch.tensor(ctx.seg_start_pos, dtype=torch.int32, device="cuda")
     q = torch.randn(T, H * (dn + dr), device="cuda", dtype=torch.bfloat16) * 0.3
-    gate = torch.randn(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    gate = torch.randn(T, H * dv, device="cuda", dtype=torch.bfloat16) if gated else None
     wuk = torch.randn(H * dn, rank, device="cuda", dtype=torch.bfloat16) * 0.05
     wuv = torch.randn(H * dv, rank, device="cuda", dtype=torch.bfloat16) * 0.05
     wuk_t = wuk.view(H, dn, rank).transpose(1, 2).contiguous()
     out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
-    us = kb.timed_chain(lambda i: ops.latent_attention(out, q, gate, caches[i % copies], wuk, wuv, ctx, table, H, dn, dr, dv, rank, page, 0,
+    us = kb.timed_chain(lambda i: ops.latent_attention(out, q, gate, caches[i % copies], wuk, wuv, ctx, table, H, dn, dr, dv, rank, page, window,
                                                        ATTN["scale"], wuk_t=wuk_t), launches=8)
-    pairs = sum(n * (ctx_len - n) + n * (n + 1) // 2 for n in seg_lens)                 # (query, key) pairs per head
+    seen = lambda pos: min(pos + 1, window) if window else pos + 1                      # keys a query at `pos` sees
+    pairs = sum(seen(ctx_len - n + i) for n in seg_lens for i in range(n))              # (query, key) pairs per head
     flops = H * pairs * (2.0 * (rank + dr) + 2.0 * rank) + T * H * 2.0 * rank * (dn + dv)
-    return kb._figures(us, S * ctx_len * row_bytes + (q.numel() + gate.numel() + out.numel()) * 2, flops, peaks)
+    rows = sum(min(ctx_len, window + n - 1) if window else ctx_len for n in seg_lens)   # cache rows the step must read
+    return kb._figures(us, rows * row_bytes + (q.numel() + (gate.numel() if gated else 0) + out.numel()) * 2, flops, peaks)
 
 
 def scan_case(kind, seg_lens, peaks) -> dict:
@@ -461,6 +464,182 @@ def run_tubazen(args, peaks) -> dict:
     return res
 
 
+# ------------------------------------------------------------------ Lugizen
+# Latent attention as above with a 768-wide latent for the queries and a window of 1,024; a delta rule of 16 value heads of 128 on
+# 8 query/key heads of 128 with convolutions of four taps and low-rank decays and gates of rank 64; rotary attention with
+# unit-normed queries and keys, 16 heads of 128 on 4 key/value heads, values blended between layers; 64 experts of 1,408 of which
+# 6 serve a token, or a dense feed-forward of the same active size; a convolution of four taps ahead of every mixer.
+LUG_LATENT = dict(ATTN, q_rank=768, mask={"size": 1024})
+LUG_DELTA = {"heads": 16, "kv_heads": 8, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+LUG_ATTN = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 10000.0, "dims": 64}, "v_mix": True}
+LUG_MOE = {"kind": "moe", "expert": {"ff": 1408}, "router": {"experts": 64, "top": 6}}
+LUG_DENSE = {"kind": "dense", "ff": 6 * 1408}
+
+
+def lugizen_config(layers_per_kind: int) -> dict:
+    kinds = [("latent_attention", LUG_LATENT, LUG_DENSE), ("channel_delta", LUG_DELTA, LUG_MOE), ("attention", LUG_ATTN, LUG_MOE)]
+    layers = [{"type": k, "mixer": m, "mlp": f} for _ in range(layers_per_kind) for k, m, f in kinds]
+    return {"architecture": "Lugizen", "vocab": VOCAB, "width": WIDTH, "norm": {"eps": 1e-5}, "canon": {"taps": 4}, "layers": layers}
+
+
+def lugizen_llama_config(n_layers: int) -> dict:
+    return {"architectures": ["LlamaForCausalLM"], "vocab_size": VOCAB, "hidden_size": WIDTH, "intermediate_size": LUG_DENSE["ff"],
+            "num_hidden_layers": n_layers, "num_attention_heads": 16, "num_key_value_heads": 4, "head_dim": 128,
+            "max_position_embeddings": 8192, "rms_norm_eps": 1e-5, "rope_theta": 10000.0, "tie_word_embeddings": False}
+
+
+def plain_attention_case(seg_lens, ctx_len, peaks, page=16) -> dict:
+    """Softmax attention over cache rows [keys | values] without a bias table (the preparing kernel excluded)."""
+    a = LUG_ATTN
+    H, G, n, dv = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
+    S, T = len(seg_lens), sum(seg_lens)
+    blocks = -(-ctx_len // page)
+    width = G * (n + dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * ctx_len * width * 2)) + 1))
+    caches = torch.randn(copies, S * blocks + 1, page, width, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(S * blocks, dtype=torch.int32, device="cuda").view(S, blocks)
+    ctx = _ctx(seg_lens, [ctx_len - m for m in seg_lens])
+    ctx.seg_len, ctx.seg_start_pos, ctx.max_ctx_len, ctx.captured = list(seg_lens), [ctx_len - m for m in seg_lens], ctx_len, False
+    ctx.seg_pos0 = torch.tensor(ctx.seg_start_pos, dtype=torch.int32, device="cuda")
+    q = torch.randn(T, H * n, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
+    none = torch.zeros(H, 1, device="cuda", dtype=torch.float32)
+    us = kb.timed_chain(lambda i: ops.bias_attention(out, q, caches[i % copies], ctx, table, H, G, n, dv, page, a["scale"], None, None, None,
+                                                     1.0, table_of_distances=none), launches=8)
+    pairs = sum(m * (ctx_len - m) + m * (m + 1) // 2 for m in seg_lens)
+    return kb._figures(us, S * ctx_len * width * 2 + (q.numel() + out.numel()) * 2, H * pairs * (2.0 * n + 2.0 * dv), peaks)
+
+
+def rot_norm_prepare_case(T, peaks, page=16) -> dict:
+    """Rotation, unit norms, temperature, blended values and the cache write of T tokens of one request."""
+    a = LUG_ATTN
+    H, G, n, dv, rot = a["heads"], a["kv_heads"], a["dim"], a["vdim"], a["rot"]["dims"]
+    cols, width = (H + G) * n + G * dv, G * (n + dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (T * (cols * 4 + G * dv * 4 + width * 2 + H * n * 2))) + 1))
+    projs = torch.randn(copies, T, cols, device="cuda", dtype=torch.float32)
+    firsts = torch.randn(copies, T, G * dv, device="cuda", dtype=torch.float32)
+    blocks = -(-T // page)
+    caches = torch.zeros(copies, blocks + 1, page, width, device="cuda", dtype=torch.bfloat16)
+    table = torch.arange(blocks, dtype=torch.int32, device="cuda").view(1, blocks)
+    ctx = _ctx([T], [0])
+    ang = torch.arange(T, device="cuda", dtype=torch.float32)[:, None] * torch.rand(rot // 2, device="cuda")[None, :]
+    cos_sin = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+    temp = torch.rand(H, device="cuda") + 0.5
+    q = torch.empty(copies, T, H * n, device="cuda", dtype=torch.bfloat16)
+    us = kb.timed_chain(lambda i: ops.rot_norm_prepare(q[i % copies], projs[i % copies], 0, H * n, (H + G) * n, caches[i % copies], cos_sin, rot, True,
+                                                       1e-5, temp, firsts[i % copies], 0.4, ctx, table, H, G, n, dv, page), launches=8)
+    return kb._figures(us, T * (cols * 4 + G * dv * 4 + width * 2 + H * n * 2), 0.0, peaks)
+
+
+def channel_delta_case(seg_lens, peaks, scan_only=False) -> dict:
+    """The delta rule on the decayed state: its chain (convolutions with SiLU, decays, gate pre-activations, operands, recurrence,
+    norm and gate), or (scan_only) the recurrence's kernel alone."""
+    m = LUG_DELTA
+    H, G, dk, dv, taps, ra, rg = m["heads"], m["kv_heads"], m["dim"], m["vdim"], m["conv"], m["decay_rank"], m["gate_rank"]
+    S, T = len(seg_lens), sum(seg_lens)
+    ctx = _ctx(seg_lens, [0] * S)
+    C = 2 * G * dk + H * dv
+    n_state = ops.channel_scan_state_floats(H, dk, dv)
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (S * n_state * 4)) + 1))
+    states = torch.zeros(copies, S, n_state, device="cuda", dtype=torch.float32)
+    tails = torch.zeros(S, (taps - 1) * C, device="cuda", dtype=torch.float32)
+    f32 = dict(device="cuda", dtype=torch.float32)
+    proj = torch.randn(T, C + H + ra + rg, **f32) * 0.3
+    conv_w = torch.randn(C, taps, **f32) * 0.3
+    a_up, dt_bias, rate = torch.randn(ra, H * dk, **f32) * 0.1, torch.randn(H * dk, **f32) - 2, torch.rand(H * dk, **f32)
+    g_up, nw = torch.randn(rg, H * dv, **f32) * 0.1, torch.ones(H * dv, **f32)
+    conv, decay, gate = torch.empty(T, C, **f32), torch.empty(T, H * dk, **f32), torch.empty(T, H * dv, **f32)
+    qh, kb_, ug = (torch.empty(T, H * dk, **f32) for _ in range(3))
+    y = torch.empty(T, H * dv, **f32)
+    out = torch.empty(T, H * dv, device="cuda", dtype=torch.bfloat16)
+
+    def prepare():
+        ops.conv_state(conv, proj[:, :C], conv_w, None, tails, ctx, act=True)
+        ops.channel_gates(decay, proj[:, C + H: C + H + ra], a_up, dt_bias, False, ops.GATE_EXP_NEG_SOFTPLUS, 0.0, rate=rate)
+        ops.channel_gates(gate, proj[:, C + H + ra:], g_up, None, False, ops.GATE_LINEAR, 0.0)
+        ops.delta_operands(qh, kb_, ug, conv[:, : G * dk], conv[:, G * dk: 2 * G * dk], proj[:, C: C + H], decay, H, G, dk, 1e-6, dk ** -0.5)
+    prepare()
+
+    def run(i):
+        if not scan_only:
+            prepare()
+        ops.channel_scan(y, qh, kb_, conv[:, 2 * G * dk:], decay, kb_, ug, 1.0, states[i % copies], ctx, H, dk, dv)
+        if not scan_only:
+            ops.head_norm_gate(out, y, gate, nw, H, 1e-5, ops.HEAD_GATE_SIGMOID)
+
+    us = kb.timed_chain(run, launches=6)
+    vecs = 4 * H * dk + 2 * H * dv                           # the scan reads decay, written key, reading key, query and value; writes the output
+    nbytes = 2 * S * n_state * 4 + T * vecs * 4
+    if not scan_only:
+        nbytes += T * ((C + H + ra + rg) * 4 + H * dv * 2)
+    return kb._figures(us, nbytes, 8.0 * T * H * dk * dv, peaks)
+
+
+def stream_passes_case(T, peaks) -> dict:
+    """The two passes a post-norm layer makes over the stream beside its products: the convolution ahead of the mixer (float32 stream
+    in, compute type out) and the norm of a sublayer's output added to the stream (with the stream's copy in the compute type)."""
+    d, taps = WIDTH, 4
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (T * d * 12)) + 1))
+    res = torch.randn(copies, T, d, device="cuda", dtype=torch.float32)
+    y = torch.randn(copies, T, d, device="cuda", dtype=torch.bfloat16)
+    h = torch.empty(copies, T, d, device="cuda", dtype=torch.bfloat16)
+    w = torch.randn(d, taps, device="cuda", dtype=torch.float32) * 0.3
+    g = torch.ones(d, device="cuda", dtype=torch.float32)
+    tails = torch.zeros(1, (taps - 1) * d, device="cuda", dtype=torch.float32)
+    ctx = _ctx([T], [0])
+    conv_us = kb.timed_chain(lambda i: ops.conv_state(h[i % copies], res[i % copies], w, None, tails, ctx, act=False, add_input=True), launches=8)
+    norm_us = kb.timed_chain(lambda i: ops.post_rmsnorm_add(res[i % copies], y[i % copies], g, 1e-5, cast=h[i % copies]), launches=8)
+    return {"conv_input": kb._figures(conv_us, T * d * 6, 0.0, peaks), "norm_on_output": kb._figures(norm_us, T * d * 12, 0.0, peaks)}
+
+
+def add_rmsnorm_case(T, peaks) -> dict:
+    """The pre-norm decoders' pass over the stream: the pending delta added and the normed rows written."""
+    d = WIDTH
+    copies = max(2, min(8, int(2.5 * kb.L2_BYTES // (T * d * 12)) + 1))
+    res = torch.randn(copies, T, d, device="cuda", dtype=torch.float32)
+    y = torch.randn(copies, T, d, device="cuda", dtype=torch.bfloat16)
+    h = torch.empty(copies, T, d, device="cuda", dtype=torch.bfloat16)
+    g = torch.ones(d, device="cuda", dtype=torch.float32)
+    us = kb.timed_chain(lambda i: ops.add_rmsnorm(h[i % copies], res[i % copies], y[i % copies], g, 1e-5), launches=8)
+    return kb._figures(us, T * d * 12, 0.0, peaks)
+
+
+def run_lugizen(args, peaks) -> dict:
+    n_layers = 3 * args.layers_per_kind
+    res = {"lugizen": model_throughput(lugizen_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
+           "deganex_equal_size": model_throughput(deganex_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
+           "llama_equal_size": model_throughput(lugizen_llama_config(n_layers), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup)}
+    T, B, C = args.prefill_tokens, args.batch, args.ctx
+    W = LUG_LATENT["mask"]["size"]
+    res["kernels"] = {
+        f"latent_attention_window{W}_prefill_t{T}": latent_attention_case([T], T, peaks, window=W, gated=False),
+        f"latent_attention_window{W}_decode_b{B}_ctx{C}": latent_attention_case([1] * B, C, peaks, window=W, gated=False),
+        f"attention_prefill_t{T}": plain_attention_case([T], T, peaks), f"attention_decode_b{B}_ctx{C}": plain_attention_case([1] * B, C, peaks),
+        f"rot_norm_prepare_t{T}": rot_norm_prepare_case(T, peaks), f"rot_norm_prepare_t{B}": rot_norm_prepare_case(B, peaks),
+        f"channel_delta_prefill_t{T}": channel_delta_case([T], peaks), f"channel_delta_decode_b{B}": channel_delta_case([1] * B, peaks),
+        f"channel_delta_scan_alone_prefill_t{T}": channel_delta_case([T], peaks, True),
+        f"channel_delta_scan_alone_decode_b{B}": channel_delta_case([1] * B, peaks, True),
+        f"experts_prefill_t{T}": experts_case(T, peaks), f"experts_decode_b{B}": experts_case(B, peaks),
+        f"stream_passes_t{T}": stream_passes_case(T, peaks), f"stream_passes_t{B}": stream_passes_case(B, peaks),
+    }
+    # the like kernels of the closest designs: Deganex's latent attention (no window, gated) and experts (the same kernels), Tubazen's
+    # attention with a distance bias, its preparing kernel and its delta rule's chain, the pre-norm decoders' norm pass
+    res["like_kernels"] = {
+        f"latent_attention_prefill_t{T}": latent_attention_case([T], T, peaks), f"latent_attention_decode_b{B}_ctx{C}": latent_attention_case([1] * B, C, peaks),
+        f"bias_attention_prefill_t{T}": bias_attention_case([T], T, peaks), f"bias_attention_decode_b{B}_ctx{C}": bias_attention_case([1] * B, C, peaks),
+        f"bias_prepare_t{T}": bias_prepare_case(T, peaks), f"bias_prepare_t{B}": bias_prepare_case(B, peaks),
+        f"delta_scan_prefill_t{T}": channel_scan_case("delta", [T], peaks), f"delta_scan_decode_b{B}": channel_scan_case("delta", [1] * B, peaks),
+        f"delta_scan_alone_prefill_t{T}": channel_scan_case("delta", [T], peaks, True),
+        f"delta_scan_alone_decode_b{B}": channel_scan_case("delta", [1] * B, peaks, True),
+        f"add_rmsnorm_t{T}": add_rmsnorm_case(T, peaks), f"add_rmsnorm_t{B}": add_rmsnorm_case(B, peaks),
+    }
+    from .config import LlamaConfig
+    like = kb.headline_kernels(LlamaConfig.from_dict(lugizen_llama_config(n_layers)), B, C, T, peaks)
+    ops.check_kernel_errors()
+    res["llama_kernels"] = {k: v for k, v in like.items() if "attention" in k or "gate_up" in k or "down" in k}
+    return res
+
+
 def run(args, peaks) -> dict:
     n_layers = 3 * args.layers_per_kind
     res = {"deganex": model_throughput(deganex_config(args.layers_per_kind), args.batch, args.ctx, args.prefill_tokens, args.steps, args.warmup),
@@ -483,7 +662,7 @@ def run(args, peaks) -> dict:
 
 def main(argv=None, peaks=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    ap.add_argument("--design", default="deganex", choices=["deganex", "lotirax", "tubazen"])
+    ap.add_argument("--design", default="deganex", choices=["deganex", "lotirax", "tubazen", "lugizen"])
     ap.add_argument("--layers-per-kind", type=int, default=2)
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--ctx", type=int, default=1024)
@@ -496,6 +675,8 @@ def main(argv=None, peaks=None) -> int:
         res, model = run_lotirax(args, peaks), f"Lotirax, width {WIDTH}, 4 layers of which 2 run twice"
     elif args.design == "tubazen":
         res, model = run_tubazen(args, peaks), f"Tubazen, width {WIDTH}, {2 * args.layers_per_kind} layers"
+    elif args.design == "lugizen":
+        res, model = run_lugizen(args, peaks), f"Lugizen, width {WIDTH}, {3 * args.layers_per_kind} layers"
     else:
         res, model = run(args, peaks), f"Deganex, width {WIDTH}, {3 * args.layers_per_kind} layers"
     d = res[args.design]
