@@ -543,7 +543,9 @@ __global__ void __launch_bounds__(32 * WARPS) bias_attention_mma_kernel(BiasMmaA
   }
 }
 
-// joins a token's slices (ascending), then gate and factor.  One warp per (token, head).
+// joins a token's slices (ascending), then gate and factor.  One warp per (token, head): the lanes share out the slices for the
+// maximum, the sum and the slices' weights, and the columns for the values, whose loads for several slices are in flight together
+// (read one slice after the other, a (token, head) waited for some fifty loads in a row).  dv <= 128.
 __global__ void __launch_bounds__(128) bias_attention_merge_kernel(bf16* __restrict__ out, int ld_out, const float* __restrict__ partial,
                                                                   const int* __restrict__ seg_q_start, const int* __restrict__ seg_pos0,
                                                                   int H, int dv, int all_slices, int slice_keys,
@@ -552,23 +554,57 @@ __global__ void __launch_bounds__(128) bias_attention_merge_kernel(bf16* __restr
   pdl_launch_dependents();
   const int s = blockIdx.x, h = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
   if (h >= H) return;
-  const float* p = partial + ((size_t)s * H + h) * all_slices * (2 + dv);
+  const int stride = 2 + dv;
+  const float* p = partial + ((size_t)s * H + h) * all_slices * stride;
   const int slices = min(all_slices, seg_pos0[s] / slice_keys + 1);       // the slices that hold keys of this token
-  float M = -INFINITY;
-  for (int i = 0; i < slices; ++i) M = fmaxf(M, p[(size_t)i * (2 + dv)]);
-  float L = 0.f;
-  for (int i = 0; i < slices; ++i) L += p[(size_t)i * (2 + dv) + 1] * exp2f(p[(size_t)i * (2 + dv)] - M);
+  float M = -INFINITY, L = 0.f;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  if (slices <= 32) {                            // a lane a slice: maximum and sum are read once, the values' loads do not wait for them
+    const float mi = lane < slices ? p[(size_t)lane * stride] : -INFINITY;
+    const float li = lane < slices ? p[(size_t)lane * stride + 1] : 0.f;
+    M = warp_max(mi);
+    const float wi = exp2f(mi - M);
+    L = warp_sum(li * wi);
+#pragma unroll 8
+    for (int j = 0; j < slices; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, wi, j);
+      const float* ps = p + (size_t)j * stride + 2;
+#pragma unroll
+      for (int r = 0; r < 4; ++r) {
+        const int c = lane + 32 * r;
+        if (c < dv) acc[r] = fmaf(ps[c], wj, acc[r]);
+      }
+    }
+  } else {
+    for (int i = lane; i < slices; i += 32) M = fmaxf(M, p[(size_t)i * stride]);
+    M = warp_max(M);
+    for (int i = lane; i < slices; i += 32) L += p[(size_t)i * stride + 1] * exp2f(p[(size_t)i * stride] - M);
+    L = warp_sum(L);
+    for (int base = 0; base < slices; base += 32) {
+      const float wi = base + lane < slices ? exp2f(p[(size_t)(base + lane) * stride] - M) : 0.f;
+      const int cnt = min(32, slices - base);
+#pragma unroll 4
+      for (int j = 0; j < cnt; ++j) {
+        const float wj = __shfl_sync(0xffffffffu, wi, j);
+        const float* ps = p + (size_t)(base + j) * stride + 2;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const int c = lane + 32 * r;
+          if (c < dv) acc[r] = fmaf(ps[c], wj, acc[r]);
+        }
+      }
+    }
+  }
   const size_t t = (size_t)seg_q_start[s];
   const float inv = 1.0f / L;
-  for (int c = lane; c < dv; c += 32) {
-    float acc = 0.f;
-    for (int i = 0; i < slices; ++i) {
-      const float* ps = p + (size_t)i * (2 + dv);
-      acc = fmaf(ps[2 + c], exp2f(ps[0] - M), acc);
+#pragma unroll
+  for (int r = 0; r < 4; ++r) {
+    const int c = lane + 32 * r;
+    if (c < dv) {
+      float v = acc[r] * inv;
+      if (gate) v *= 1.0f / (1.0f + expf(-gate[t * ld_g + (size_t)h * dv + c]));
+      out[t * ld_out + (size_t)h * dv + c] = __float2bfloat16_rn(v * factor);
     }
-    float v = acc * inv;
-    if (gate) v *= 1.0f / (1.0f + expf(-gate[t * ld_g + (size_t)h * dv + c]));
-    out[t * ld_out + (size_t)h * dv + c] = __float2bfloat16_rn(v * factor);
   }
 }
 

@@ -723,8 +723,9 @@ extern "C" const char* qv_error_string(int code) {
 // ---------------------------------------------------------------- norm on a sublayer's output (post-norm blocks)
 // residual[t] += y[t] * rsqrt(mean(y[t]^2) + eps) * w     (float32; y in the compute type or float32, row stride ld_y)
 // cast[t] = residual[t] in the compute type, if cast is given: what the next sublayer's products read.
-// One block per row; the sum's order depends on d alone.
-template <typename TY, typename TO>
+// One block per row; the sum's order depends on d alone.  VEC: the row of y stays in registers and is read once, four elements
+// at a time (d a multiple of 4, at most 4 * 4 * blockDim elements, rows that start on 16 bytes).
+template <typename TY, typename TO, bool VEC>
 __global__ void __launch_bounds__(256) post_rmsnorm_add_kernel(float* __restrict__ residual, const TY* __restrict__ y, int ld_y,
                                                               const float* __restrict__ w, float eps, TO* __restrict__ cast, int d) {
   __shared__ float red[33];
@@ -734,13 +735,40 @@ __global__ void __launch_bounds__(256) post_rmsnorm_add_kernel(float* __restrict
   const TY* yr = y + (size_t)t * ld_y;
   float* res = residual + (size_t)t * d;
   float ss = 0.f;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = to_f(yr[i]); ss = fmaf(v, v, ss); }
-  const float total = block_sum(ss, red);
-  const float sc = 1.0f / sqrtf(total / (float)d + eps);
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    const float x = res[i] + to_f(yr[i]) * sc * w[i];
-    res[i] = x;
-    if (cast) cast[(size_t)t * d + i] = from_f<TO>(x);
+  if constexpr (VEC) {
+    constexpr int MAXV = 4;
+    float4 v[MAXV], r[MAXV];
+    const int nvec = d >> 2;
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      v[k] = i < nvec ? Vec4<TY>::load(yr + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      r[k] = i < nvec ? *(const float4*)(res + 4 * i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) ss += v[k].x * v[k].x + v[k].y * v[k].y + v[k].z * v[k].z + v[k].w * v[k].w;
+    const float total = block_sum(ss, red);
+    const float sc = 1.0f / sqrtf(total / (float)d + eps);
+#pragma unroll
+    for (int k = 0; k < MAXV; ++k) {
+      const int i = threadIdx.x + k * 256;
+      if (i < nvec) {
+        const float4 wv = *(const float4*)(w + 4 * i);
+        const float4 x = make_float4(r[k].x + v[k].x * sc * wv.x, r[k].y + v[k].y * sc * wv.y, r[k].z + v[k].z * sc * wv.z,
+                                     r[k].w + v[k].w * sc * wv.w);
+        *(float4*)(res + 4 * i) = x;
+        if (cast) store4(cast + (size_t)t * d + 4 * i, x);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < d; i += blockDim.x) { const float v = to_f(yr[i]); ss = fmaf(v, v, ss); }
+    const float total = block_sum(ss, red);
+    const float sc = 1.0f / sqrtf(total / (float)d + eps);
+    for (int i = threadIdx.x; i < d; i += blockDim.x) {
+      const float x = res[i] + to_f(yr[i]) * sc * w[i];
+      res[i] = x;
+      if (cast) cast[(size_t)t * d + i] = from_f<TO>(x);
+    }
   }
 }
 
@@ -748,8 +776,15 @@ extern "C" int qv_post_rmsnorm_add(float* residual, const void* y, int ld_y, con
                                    int y_dt, int cast_dt, void* stream) {
   if (T <= 0 || d <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
-#define LAUNCH_POST(TY, TO) \
-  return qv_launch(post_rmsnorm_add_kernel<TY, TO>, dim3(T), dim3(256), 0, st, residual, (const TY*)y, ld_y, w, eps, (TO*)cast, d)
+  const bool vec = d % 4 == 0 && d <= 4 * 4 * 256 && ld_y % 4 == 0 &&
+                   (((uintptr_t)residual | (uintptr_t)y | (uintptr_t)w | (uintptr_t)cast) & 15) == 0;
+#define LAUNCH_POST(TY, TO)                                                                                                        \
+  do {                                                                                                                             \
+    if (vec) return qv_launch(post_rmsnorm_add_kernel<TY, TO, true>, dim3(T), dim3(256), 0, st, residual, (const TY*)y, ld_y, w,   \
+                              eps, (TO*)cast, d);                                                                                  \
+    return qv_launch(post_rmsnorm_add_kernel<TY, TO, false>, dim3(T), dim3(256), 0, st, residual, (const TY*)y, ld_y, w, eps,      \
+                     (TO*)cast, d);                                                                                                \
+  } while (0)
   if (y_dt == QV_DT_F32 && cast_dt == QV_DT_F32) LAUNCH_POST(float, float);
   if (y_dt == QV_DT_BF16 && cast_dt == QV_DT_BF16) LAUNCH_POST(bf16, bf16);
   if (y_dt == QV_DT_F32 && cast_dt == QV_DT_BF16) LAUNCH_POST(float, bf16);

@@ -16,7 +16,7 @@
 #include "common.cuh"
 
 #define CONV_MAX_TAPS 16
-#define CONV_CHUNK 64
+#define CONV_CHUNK 16
 
 // in/out: [T, channels] with row strides and types of their own; w [channels, taps] (last column: the current token),
 // bias [channels] or null; tail [slots][(taps-1) * channels] float32, oldest input first.  act 1: SiLU of the sum, 0: the sum
@@ -37,28 +37,46 @@ __global__ void __launch_bounds__(128) conv_state_kernel(TO* __restrict__ out, i
   if (c >= channels || j0 >= len) return;
   const int j1 = j0 + CONV_CHUNK < len ? j0 + CONV_CHUNK : len;
   float* tl = tail + (size_t)seg_slot[s] * slot_stride;
-  float wt[CONV_MAX_TAPS], old[CONV_MAX_TAPS];
+  float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
+  // win[i]: the input taps - 1 - i places ahead of the token in turn; a chunk is at least as long as the longest filter reaches
+  // back, so only the first chunk reads the state
 #pragma unroll
   for (int i = 0; i < CONV_MAX_TAPS; ++i) {
     wt[i] = i < taps ? w[(size_t)c * taps + i] : 0.f;
-    old[i] = (blockIdx.z == 0 && i < taps - 1) ? tl[(size_t)i * channels + c] : 0.f;
+    win[i] = 0.f;
+    if (i < taps - 1) {
+      const int idx = j0 - (taps - 1) + i;
+      win[i] = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : tl[(size_t)(taps - 1 + idx) * channels + c];
+    }
   }
+  float old[CONV_MAX_TAPS];                      // the inputs ahead of the segment, for the state's update
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) old[i] = (blockIdx.z == 0 && i < taps - 1) ? win[i] : 0.f;
   const float b = bias ? bias[c] : 0.f;
-  // a chunk is at least as long as the longest filter, so only the first chunk reaches back into the state
-  for (int j = j0; j < j1; ++j) {
-    float acc = b, cur = 0.f;
+  float curs[CONV_CHUNK];                        // the chunk's inputs, all loads in flight before the first is used
+#pragma unroll
+  for (int jj = 0; jj < CONV_CHUNK; ++jj) curs[jj] = j0 + jj < j1 ? to_f(in[(size_t)(q0 + j0 + jj) * ld_in + c]) : 0.f;
+#pragma unroll
+  for (int jj = 0; jj < CONV_CHUNK; ++jj) {
+    if (j0 + jj >= j1) break;
+    const float cur = curs[jj];
+    float acc = b;
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
+      if (i < taps - 1) acc = fmaf(wt[i], win[i], acc);
+    }
 #pragma unroll
     for (int i = 0; i < CONV_MAX_TAPS; ++i) {
-      if (i < taps) {
-        const int idx = j - (taps - 1) + i;
-        const float v = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : old[taps - 1 + idx];
-        acc = fmaf(wt[i], v, acc);
-        if (i == taps - 1) cur = v;
-      }
+      if (i == taps - 1) acc = fmaf(wt[i], cur, acc);
+    }
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
+      if (i < taps - 2) win[i] = win[i + 1];
+      else if (i == taps - 2) win[i] = cur;
     }
     if (act) acc = acc / (1.0f + expf(-acc));
     if (add_input) acc += cur;
-    out[(size_t)(q0 + j) * ld_out + c] = from_f<TO>(acc);
+    out[(size_t)(q0 + j0 + jj) * ld_out + c] = from_f<TO>(acc);
   }
   if (blockIdx.z == 0) {
     for (int i = 0; i < taps - 1; ++i) {
