@@ -73,6 +73,96 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_kernel(float* __r
   if (lane == 0) logits[(size_t)t * (E + 1) + e] = acc;
 }
 
+// The same dot products for ROUTE_TOKENS tokens at once: a weight row is read once for all of them, and every token's sum has
+// the order route_dot gives it (a lane's elements ascending, then the warp's tree), so the logits do not depend on which kernel
+// formed them.  xs: [ROUTE_TOKENS][d] float32 in shared memory.
+#define ROUTE_TOKENS 8
+template <typename TW>
+__device__ __forceinline__ void route_dot_tokens(const TW* __restrict__ w, const float* __restrict__ xs, int d, int lane, float (&acc)[ROUTE_TOKENS]) {
+  constexpr int VEC = 16 / (int)sizeof(TW);
+#pragma unroll
+  for (int t = 0; t < ROUTE_TOKENS; ++t) acc[t] = 0.f;
+  int i = 0;
+  if ((d % VEC) == 0 && (((uintptr_t)w) & 15) == 0) {
+    for (i = lane * VEC; i + 7 * 32 * VEC < d; i += 8 * 32 * VEC) {
+      uint4 wv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) wv[u] = *(const uint4*)(w + i + u * 32 * VEC);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const TW* p = (const TW*)&wv[u];
+        float wf[VEC];
+#pragma unroll
+        for (int k = 0; k < VEC; ++k) wf[k] = to_f(p[k]);
+#pragma unroll
+        for (int t = 0; t < ROUTE_TOKENS; ++t) {
+          const float4* x4 = (const float4*)(xs + (size_t)t * d + i + u * 32 * VEC);
+#pragma unroll
+          for (int k4 = 0; k4 < VEC / 4; ++k4) {
+            const float4 xv = x4[k4];
+            acc[t] = fmaf(wf[4 * k4], xv.x, acc[t]); acc[t] = fmaf(wf[4 * k4 + 1], xv.y, acc[t]);
+            acc[t] = fmaf(wf[4 * k4 + 2], xv.z, acc[t]); acc[t] = fmaf(wf[4 * k4 + 3], xv.w, acc[t]);
+          }
+        }
+      }
+    }
+    for (; i < d; i += 32 * VEC) {
+      const uint4 wv = *(const uint4*)(w + i);
+      const TW* p = (const TW*)&wv;
+#pragma unroll
+      for (int k = 0; k < VEC; ++k) {
+        const float wf = to_f(p[k]);
+#pragma unroll
+        for (int t = 0; t < ROUTE_TOKENS; ++t) acc[t] = fmaf(wf, xs[(size_t)t * d + i + k], acc[t]);
+      }
+    }
+  } else {
+    for (i = lane; i + 7 * 32 < d; i += 8 * 32) {
+      float wv[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) wv[u] = to_f(w[i + u * 32]);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+#pragma unroll
+        for (int t = 0; t < ROUTE_TOKENS; ++t) acc[t] = fmaf(wv[u], xs[(size_t)t * d + i + u * 32], acc[t]);
+      }
+    }
+    for (; i < d; i += 32) {
+      const float wf = to_f(w[i]);
+#pragma unroll
+      for (int t = 0; t < ROUTE_TOKENS; ++t) acc[t] = fmaf(wf, xs[(size_t)t * d + i], acc[t]);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < ROUTE_TOKENS; ++t) acc[t] = warp_sum(acc[t]);
+}
+
+// Many tokens: a CTA takes ROUTE_TOKENS tokens and eight rows, so the router's matrix is read once per group of tokens
+// instead of once per token.  d a multiple of 4 (16-byte reads of the tokens' rows in shared memory).
+template <typename T, typename TW>
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_logits_tokens_kernel(float* __restrict__ logits, const T* __restrict__ h, int ld_h,
+                                                                             const TW* __restrict__ wr, const TW* __restrict__ wg, int d,
+                                                                             int E, int T_all) {
+  extern __shared__ __align__(16) float xs_tokens[];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t0 = blockIdx.x * ROUTE_TOKENS, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < ROUTE_TOKENS * d; i += blockDim.x) {
+    const int t = i / d, c = i - t * d;
+    xs_tokens[i] = t0 + t < T_all ? to_f(h[(size_t)(t0 + t) * ld_h + c]) : 0.f;
+  }
+  __syncthreads();
+  const int e = blockIdx.y * ROUTE_WARPS + warp;
+  if (e >= E + (wg ? 1 : 0)) return;
+  float acc[ROUTE_TOKENS];
+  route_dot_tokens(e < E ? wr + (size_t)e * d : wg, xs_tokens, d, lane, acc);
+  if (lane == 0) {
+#pragma unroll
+    for (int t = 0; t < ROUTE_TOKENS; ++t)
+      if (t0 + t < T_all) logits[(size_t)(t0 + t) * (E + 1) + e] = acc[t];
+  }
+}
+
 // pre: logits worked out by moe_logits_kernel ([T][E + 1]), or null: then this kernel forms them itself.
 template <typename T, typename TW>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __restrict__ top_idx, float* __restrict__ top_w, float* __restrict__ gate_out,
@@ -127,8 +217,9 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) moe_route_kernel(int* __rest
   for (int j = lane; j < top; j += 32) top_w[(size_t)t * top + j] /= denom;
 }
 
-// logits_ws: room for T * (E + 1) floats, or null.  With it, steps of up to 256 tokens form the logits in a launch of
-// their own over (tokens x groups of eight rows) CTAs; the result is the same either way (same sums, same order).
+// logits_ws: room for T * (E + 1) floats, or null.  With it, the logits are formed in a launch of their own: for steps of up to
+// 256 tokens over (tokens x groups of eight rows) CTAs, for longer ones over (groups of eight tokens x groups of eight rows); the
+// result is the same whichever kernel forms them (same sums, same order).
 extern "C" int qv_moe_route(int* top_idx, float* top_w, float* gate_out, const void* h, int ld_h, const void* wr, const void* wg,
                             float* logits_ws, int T, int d, int E, int top, int dt, int w_dt, void* stream) {
   if (T <= 0) return 0;
@@ -137,16 +228,27 @@ extern "C" int qv_moe_route(int* top_idx, float* top_w, float* gate_out, const v
   const size_t smem = (size_t)(E + d) * sizeof(float);
   if (smem > 48 * 1024) return QV_ERR_TOO_LARGE;
   const bool split = logits_ws && T <= 256;
+  // more tokens: the logits by groups of tokens, where the group's rows fit shared memory
+  const size_t tsmem = (size_t)ROUTE_TOKENS * d * sizeof(float);
+  const bool tokens = logits_ws && !split && d % 4 == 0 && tsmem <= 160 * 1024;
   const dim3 lgrid(T, (E + (wg ? 1 : 0) + ROUTE_WARPS - 1) / ROUTE_WARPS);
+  const dim3 tgrid((T + ROUTE_TOKENS - 1) / ROUTE_TOKENS, (E + (wg ? 1 : 0) + ROUTE_WARPS - 1) / ROUTE_WARPS);
 #define ROUTE(TT, TW)                                                                                                        \
   do {                                                                                                                       \
     if (split) {                                                                                                             \
       const int rc = qv_launch(moe_logits_kernel<TT, TW>, lgrid, dim3(ROUTE_WARPS * 32), (size_t)d * sizeof(float), st, logits_ws, \
                                (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E);                                      \
       if (rc) return rc;                                                                                                     \
+    } else if (tokens) {                                                                                                     \
+      if (tsmem > 48 * 1024)                                                                                                 \
+        cudaFuncSetAttribute(moe_logits_tokens_kernel<TT, TW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tsmem);     \
+      const int rc = qv_launch(moe_logits_tokens_kernel<TT, TW>, tgrid, dim3(ROUTE_WARPS * 32), tsmem, st, logits_ws,        \
+                               (const TT*)h, ld_h, (const TW*)wr, (const TW*)wg, d, E, T);                                   \
+      if (rc) return rc;                                                                                                     \
     }                                                                                                                        \
     return qv_launch(moe_route_kernel<TT, TW>, dim3(T), dim3(ROUTE_WARPS * 32), smem, st, top_idx, top_w, gate_out, (const TT*)h, \
-                     ld_h, (const TW*)wr, (const TW*)wg, d, E, top, split ? (const float*)logits_ws : (const float*)nullptr); \
+                     ld_h, (const TW*)wr, (const TW*)wg, d, E, top,                                                          \
+                     (split || tokens) ? (const float*)logits_ws : (const float*)nullptr);                                   \
   } while (0)
   if (dt == QV_DT_F32 && w_dt == QV_DT_F32) ROUTE(float, float);
   if (dt == QV_DT_BF16 && w_dt == QV_DT_BF16) ROUTE(bf16, bf16);

@@ -906,7 +906,8 @@ def moe_route(top_idx, top_w, gate_out, h, w_router, w_gate) -> None:
     T, d = h.shape
     E, top = w_router.shape[0], top_idx.shape[1]
     assert h.stride(1) == 1 and w_router.is_contiguous() and w_router.shape[1] == d and top_idx.is_contiguous() and top_w.is_contiguous()
-    few = T <= 256                   # few tokens: the logits in a launch of their own, spread over more SMs
+    # the logits in a launch of their own: few tokens spread over more SMs, many share the router's rows in groups of eight
+    few = T <= 256 or (d % 4 == 0 and 8 * d * 4 <= 160 * 1024)
     ws = torch.empty(T * (E + 1), device=h.device, dtype=torch.float32) if few else None
     rc = _lib("moe").qv_moe_route(_ptr(top_idx), _ptr(top_w), _ptr(gate_out), _ptr(h), h.stride(0), _ptr(w_router), _ptr(w_gate),
                                   _ptr(ws), T, d, E, top, dt_code(h.dtype), dt_code(w_router.dtype), _stream())

@@ -208,6 +208,25 @@ def test_routed_feed_forward_alone(experts, top, ff, T, dtype):
     close(part.forward(x.to(dtype).to(DEV), None).float(), want, dtype, "experts")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("d,E,top", [(72, 6, 2), (2048, 64, 6), (70, 5, 5)])
+def test_the_router_does_not_depend_on_the_number_of_tokens(d, E, top, dtype):
+    """Long steps form the logits by groups of tokens, short ones token by token: choices and weights are the same bit for bit."""
+    x = (rnd(600, d, seed=d) * 0.5).to(dtype).to(DEV)
+    w = (rnd(E, d, seed=E) * d ** -0.5 * 4).to(dtype).to(DEV)
+
+    def route(rows):
+        idx = torch.empty(rows.shape[0], top, device=DEV, dtype=torch.int32)
+        wts = torch.empty(rows.shape[0], top, device=DEV, dtype=torch.float32)
+        ops.moe_route(idx, wts, None, rows, w, None)
+        return idx, wts
+    whole_idx, whole_w = route(x)
+    parts = [route(x[a:b]) for a, b in ((0, 1), (1, 200), (200, 257), (257, 600))]
+    assert torch.equal(whole_idx, torch.cat([p[0] for p in parts])) and torch.equal(whole_w, torch.cat([p[1] for p in parts]))
+    z = x.double().cpu() @ w.double().cpu().T
+    assert torch.equal(whole_idx[:, 0].cpu().long(), z.argmax(dim=1)) or dtype == torch.bfloat16
+
+
 # ---------------------------------------------------------------------------------------------- attention
 
 ATTN_CASES = [lh.attn(), lh.attn(heads=6, kv_heads=1, dim=8, vdim=8, rot_dims=8), lh.attn(heads=17, kv_heads=1, dim=6, vdim=10, rot_dims=2),
