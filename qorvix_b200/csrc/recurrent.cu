@@ -21,8 +21,8 @@
 // in/out: [T, channels] with row strides and types of their own; w [channels, taps] (last column: the current token),
 // bias [channels] or null; tail [slots][(taps-1) * channels] float32, oldest input first.  act 1: SiLU of the sum, 0: the sum
 // as it is; add_input 1: the current input is added to the result (out = in + conv(in), after the activation).
-// grid (segments, channel tiles, time chunks).
-template <typename TI, typename TO>
+// grid (segments, channel tiles, time chunks).  MT: the most taps this instance takes (its arrays stay in registers).
+template <typename TI, typename TO, int MT>
 __global__ void __launch_bounds__(128) conv_state_kernel(TO* __restrict__ out, int ld_out, const TI* __restrict__ in, int ld_in,
                                                          const float* __restrict__ w, const float* __restrict__ bias,
                                                          float* __restrict__ tail, long long slot_stride,
@@ -37,11 +37,14 @@ __global__ void __launch_bounds__(128) conv_state_kernel(TO* __restrict__ out, i
   if (c >= channels || j0 >= len) return;
   const int j1 = j0 + CONV_CHUNK < len ? j0 + CONV_CHUNK : len;
   float* tl = tail + (size_t)seg_slot[s] * slot_stride;
-  float wt[CONV_MAX_TAPS], win[CONV_MAX_TAPS];
+  float curs[CONV_CHUNK];                        // the chunk's inputs, all loads in flight before the first is used
+#pragma unroll
+  for (int jj = 0; jj < CONV_CHUNK; ++jj) curs[jj] = j0 + jj < j1 ? to_f(in[(size_t)(q0 + j0 + jj) * ld_in + c]) : 0.f;
+  float wt[MT], win[MT];
   // win[i]: the input taps - 1 - i places ahead of the token in turn; a chunk is at least as long as the longest filter reaches
   // back, so only the first chunk reads the state
 #pragma unroll
-  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+  for (int i = 0; i < MT; ++i) {
     wt[i] = i < taps ? w[(size_t)c * taps + i] : 0.f;
     win[i] = 0.f;
     if (i < taps - 1) {
@@ -49,40 +52,51 @@ __global__ void __launch_bounds__(128) conv_state_kernel(TO* __restrict__ out, i
       win[i] = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : tl[(size_t)(taps - 1 + idx) * channels + c];
     }
   }
-  float old[CONV_MAX_TAPS];                      // the inputs ahead of the segment, for the state's update
+  if (blockIdx.z == 0) {
+    // the state after this segment: its last taps - 1 inputs, or, of a segment shorter than that, what is left of the old state
+    // ahead of its own inputs.  Written now from values in registers (only this thread reads or writes these entries).
 #pragma unroll
-  for (int i = 0; i < CONV_MAX_TAPS; ++i) old[i] = (blockIdx.z == 0 && i < taps - 1) ? win[i] : 0.f;
+    for (int i = 0; i < MT - 1; ++i) {
+      if (i < taps - 1) {
+        const int idx = len - (taps - 1) + i;             // place in the segment; below zero: entry len + i of the old state
+        float v = 0.f;
+        if (idx < 0) {
+#pragma unroll
+          for (int k = 0; k < MT - 1; ++k)
+            if (k == len + i) v = win[k];
+        } else if (idx < CONV_CHUNK) {
+#pragma unroll
+          for (int k = 0; k < CONV_CHUNK; ++k)
+            if (k == idx) v = curs[k];
+        } else {
+          v = to_f(in[(size_t)(q0 + idx) * ld_in + c]);
+        }
+        tl[(size_t)i * channels + c] = v;
+      }
+    }
+  }
   const float b = bias ? bias[c] : 0.f;
-  float curs[CONV_CHUNK];                        // the chunk's inputs, all loads in flight before the first is used
-#pragma unroll
-  for (int jj = 0; jj < CONV_CHUNK; ++jj) curs[jj] = j0 + jj < j1 ? to_f(in[(size_t)(q0 + j0 + jj) * ld_in + c]) : 0.f;
 #pragma unroll
   for (int jj = 0; jj < CONV_CHUNK; ++jj) {
     if (j0 + jj >= j1) break;
     const float cur = curs[jj];
     float acc = b;
 #pragma unroll
-    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
+    for (int i = 0; i < MT - 1; ++i) {
       if (i < taps - 1) acc = fmaf(wt[i], win[i], acc);
     }
 #pragma unroll
-    for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    for (int i = 0; i < MT; ++i) {
       if (i == taps - 1) acc = fmaf(wt[i], cur, acc);
     }
 #pragma unroll
-    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) {
+    for (int i = 0; i < MT - 1; ++i) {
       if (i < taps - 2) win[i] = win[i + 1];
       else if (i == taps - 2) win[i] = cur;
     }
     if (act) acc = acc / (1.0f + expf(-acc));
     if (add_input) acc += cur;
     out[(size_t)(q0 + j0 + jj) * ld_out + c] = from_f<TO>(acc);
-  }
-  if (blockIdx.z == 0) {
-    for (int i = 0; i < taps - 1; ++i) {
-      const int idx = len - (taps - 1) + i;
-      tl[(size_t)i * channels + c] = idx >= 0 ? to_f(in[(size_t)(q0 + idx) * ld_in + c]) : old[taps - 1 + idx];
-    }
   }
 }
 
@@ -95,8 +109,13 @@ extern "C" int qv_conv_state(void* out, int ld_out, const void* in, int ld_in, c
   if (chunks > 65535 || (channels + 127) / 128 > 65535) return QV_ERR_TOO_LARGE;
   dim3 grid(S, (channels + 127) / 128, chunks);
 #define LAUNCH_CONV(TI, TO)                                                                                                    \
-  return qv_launch(conv_state_kernel<TI, TO>, grid, dim3(128), 0, (cudaStream_t)stream, (TO*)out, ld_out, (const TI*)in, ld_in, w, \
-                   bias, tail, slot_stride, seg_q_start, seg_slot, channels, taps, act, add_input)
+  do {                                                                                                                         \
+    if (taps <= 4)                                                                                                             \
+      return qv_launch(conv_state_kernel<TI, TO, 4>, grid, dim3(128), 0, (cudaStream_t)stream, (TO*)out, ld_out, (const TI*)in, \
+                       ld_in, w, bias, tail, slot_stride, seg_q_start, seg_slot, channels, taps, act, add_input);              \
+    return qv_launch(conv_state_kernel<TI, TO, CONV_MAX_TAPS>, grid, dim3(128), 0, (cudaStream_t)stream, (TO*)out, ld_out,     \
+                     (const TI*)in, ld_in, w, bias, tail, slot_stride, seg_q_start, seg_slot, channels, taps, act, add_input); \
+  } while (0)
   if (in_dt == QV_DT_F32 && out_dt == QV_DT_F32) LAUNCH_CONV(float, float);
   if (in_dt == QV_DT_BF16 && out_dt == QV_DT_BF16) LAUNCH_CONV(bf16, bf16);
   if (in_dt == QV_DT_F32 && out_dt == QV_DT_BF16) LAUNCH_CONV(float, bf16);
