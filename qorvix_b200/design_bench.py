@@ -660,7 +660,8 @@ def run(args, peaks) -> dict:
     return res
 
 
-def main(argv=None, peaks=None) -> int:
+def main(argv=None, peaks=None, extra=None) -> int:
+    """extra: a callable whose dict (the clocks sampled during the run, for instance) joins the JSON line."""
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("--design", default="deganex", choices=["deganex", "lotirax", "tubazen", "lugizen"])
     ap.add_argument("--layers-per-kind", type=int, default=2)
@@ -680,6 +681,8 @@ def main(argv=None, peaks=None) -> int:
     else:
         res, model = run(args, peaks), f"Deganex, width {WIDTH}, {3 * args.layers_per_kind} layers"
     d = res[args.design]
+    if extra is not None:
+        res = dict(res, **extra())
     print(json.dumps({"metric": f"{args.design}_decode_tokens_per_s", "value": d["decode_tok_s"], "unit": "tokens/s", "n_gpus": 1, "dtype": "bf16",
                       "data": "synthetic (random weights and tokens)", "peaks": peaks,
                       "config": {"model": model, "batch": args.batch, "ctx": args.ctx,
